@@ -1,0 +1,94 @@
+// Shared by every kernel file: element types, small reductions, error reporting.
+//
+// Launchers are plain C functions taking raw device pointers and a stream, so a
+// library builds in seconds with nvcc alone and loads through ctypes. A launcher
+// returns 0, a CUDA error code (> 0) or ABK_REFUSED (< 0: the sizes are not ones
+// this kernel takes; abk_last_error() says why).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define ABK_REFUSED (-1)
+enum { ABK_F32 = 0, ABK_BF16 = 1 };
+
+#ifdef ABK_DEFINE_ERROR
+static thread_local char abk_error_text[512];
+extern "C" const char *abk_last_error() { return abk_error_text; }
+#define ABK_REFUSE(...)                                                  \
+    do {                                                                 \
+        snprintf(abk_error_text, sizeof abk_error_text, __VA_ARGS__);    \
+        return ABK_REFUSED;                                              \
+    } while (0)
+#endif
+
+#define ABK_LAUNCH_RESULT() ((int)cudaGetLastError())
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float *scratch) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < n_warps ? scratch[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float *scratch) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < n_warps ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Where a position of a sequence lies in a paged cache.
+//   tokens_per_page keys per page; a sequence's pages are listed in its row of the page table.
+//   ring_pages > 0: the sequence keeps only that many pages and position p lives in
+//   logical page (p / tokens_per_page) % ring_pages (a window of the most recent keys).
+struct PagedCache {
+    const int *page_table;  // [slots, table_width]
+    int table_width;
+    int ring_pages;         // 0: all pages are kept
+    int tokens_per_page;
+};
+__device__ __forceinline__ int cache_page(const PagedCache &c, int slot, int pos) {
+    int logical = pos / c.tokens_per_page;
+    if (c.ring_pages > 0) logical %= c.ring_pages;
+    return c.page_table[(long long)slot * c.table_width + logical];
+}
+// Element offset of (page, kv head, position, 0) in a pool laid out [pages, kv heads, tokens_per_page, head_dim].
+__device__ __forceinline__ long long cache_offset(const PagedCache &c, int page, int kv_head, int n_kv_heads, int pos,
+                                                  int head_dim) {
+    return (((long long)page * n_kv_heads + kv_head) * c.tokens_per_page + pos % c.tokens_per_page) * head_dim;
+}

@@ -1,0 +1,206 @@
+// Row-wise kernels around the matrix products: embedding, residual add + RMSNorm,
+// SwiGLU, and the preparation of q/k/v (per-head norm, rotary encoding, cache write).
+// All arithmetic is float32; only what is stored may be bfloat16.
+#define ABK_DEFINE_ERROR
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+// x[t, :] = float(table[tokens[t], :])                      (src/model.c:290-291)
+template <typename TW>
+__global__ void embed_kernel(const int *__restrict__ tokens, const TW *__restrict__ table, float *__restrict__ x,
+                             int d, int vocab, int *status) {
+    int t = blockIdx.x;
+    int tok = tokens[t];
+    bool bad = tok < 0 || tok >= vocab;
+    if (bad && threadIdx.x == 0) atomicOr(status, 1);
+    const TW *row = table + (long long)(bad ? 0 : tok) * d;
+    float *out = x + (long long)t * d;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) out[j] = bad ? 0.0f : to_float(row[j]);
+}
+
+extern "C" int abk_embed(const int *tokens, const void *table, int table_dtype, float *x, int n_tokens, int d, int vocab,
+                         int *status, void *stream) {
+    if (n_tokens <= 0) return 0;
+    int threads = d >= 1024 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (table_dtype == ABK_BF16)
+        embed_kernel<<<n_tokens, threads, 0, s>>>(tokens, (const __nv_bfloat16 *)table, x, d, vocab, status);
+    else
+        embed_kernel<<<n_tokens, threads, 0, s>>>(tokens, (const float *)table, x, d, vocab, status);
+    return ABK_LAUNCH_RESULT();
+}
+
+// ------------------------------------------------------------------ residual add + RMSNorm
+// x += y (when y is given); out = w * (x / sqrt(mean(x^2) + eps))      (src/model.c:238-244, 164-169)
+// With `rows`, output row r is made from row rows[r] of x (+ y) and x is left as it is: the
+// final norm of the rows whose logits are wanted.
+template <typename TO>
+__global__ void add_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ y, const float *__restrict__ w,
+                                   TO *__restrict__ out, const int *__restrict__ rows, int d, float eps) {
+    __shared__ float scratch[33];
+    int r = blockIdx.x;
+    long long src = rows ? rows[r] : r;
+    float *xr = x + src * d;
+    const float *yr = y ? y + src * d : nullptr;
+    bool update = yr && !rows;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float v = xr[j];
+        if (yr) v += yr[j];
+        if (update) xr[j] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    TO *o = out + (long long)r * d;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float v = xr[j];
+        if (yr && !update) v += yr[j];
+        o[j] = from_float<TO>(w[j] * (v * scale));
+    }
+}
+
+extern "C" int abk_add_rmsnorm(float *x, const float *y, const float *w, void *out, int out_dtype, const int *rows,
+                               int n_rows, int d, float eps, void *stream) {
+    if (n_rows <= 0) return 0;
+    int threads = d >= 2048 ? 512 : d >= 512 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == ABK_BF16)
+        add_rmsnorm_kernel<<<n_rows, threads, 0, s>>>(x, y, w, (__nv_bfloat16 *)out, rows, d, eps);
+    else
+        add_rmsnorm_kernel<<<n_rows, threads, 0, s>>>(x, y, w, (float *)out, rows, d, eps);
+    return ABK_LAUNCH_RESULT();
+}
+
+// ------------------------------------------------------------------ SwiGLU
+// act[t, j] = silu(gate_up[t, j]) * gate_up[t, inter + j]              (src/model.c:274-282)
+template <typename T>
+__global__ void swiglu_kernel(const T *__restrict__ gate_up, T *__restrict__ act, long long total, int inter) {
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+         e += (long long)gridDim.x * blockDim.x) {
+        long long t = e / inter;
+        int j = (int)(e - t * inter);
+        float g = to_float(gate_up[t * 2 * inter + j]);
+        float u = to_float(gate_up[t * 2 * inter + inter + j]);
+        act[e] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+extern "C" int abk_swiglu(const void *gate_up, void *act, int dtype, int n_tokens, int inter, void *stream) {
+    long long total = (long long)n_tokens * inter;
+    if (total <= 0) return 0;
+    int threads = 256;
+    long long blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == ABK_BF16)
+        swiglu_kernel<<<(int)blocks, threads, 0, s>>>((const __nv_bfloat16 *)gate_up, (__nv_bfloat16 *)act, total, inter);
+    else
+        swiglu_kernel<<<(int)blocks, threads, 0, s>>>((const float *)gate_up, (float *)act, total, inter);
+    return ABK_LAUNCH_RESULT();
+}
+
+// ------------------------------------------------------------------ q/k/v preparation
+// Per token and head (src/model.c:247-259): RMSNorm over the head with a weight shared by all
+// heads (q and k, not v), then the rotary encoding of q and k, in place; k and v are also
+// written to their place in the paged cache.
+//
+// One warp per (token, head). Heads are numbered q heads, then k heads, then v heads, as they
+// lie in a row of qkv. Tokens whose sequence index is negative are padding and are skipped.
+struct QkvPrep {
+    void *qkv;
+    int n_heads, n_kv_heads, head_dim;
+    int q_only;  // only the q heads are prepared (keys and values come from elsewhere)
+    const int *token_seq, *token_pos, *seq_slot, *seq_len_after;
+    const float *q_norm, *k_norm;
+    float eps;
+    const float *cos, *sin;  // [positions, rotary_dim / 2]; null: no rotation
+    int rotary_dim, interleaved;
+    void *k_pool, *v_pool;  // null: nothing is cached (the layer reads another layer's cache)
+    PagedCache cache;
+};
+
+#define PREP_WARPS 4
+#define MAX_HEAD_DIM 256
+
+template <typename T> __global__ void qkv_prep_kernel(QkvPrep p) {
+    __shared__ float buf[PREP_WARPS][MAX_HEAD_DIM];
+    int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int head = blockIdx.y * PREP_WARPS + warp;
+    int total_heads = p.n_heads + 2 * p.n_kv_heads;
+    if (head >= (p.q_only ? p.n_heads : total_heads)) return;
+    int seq = p.token_seq[t];
+    if (seq < 0) return;
+    int pos = p.token_pos[t];
+    int hd = p.head_dim;
+    T *row = (T *)p.qkv + ((long long)t * total_heads + head) * hd;
+    bool is_q = head < p.n_heads, is_k = !is_q && head < p.n_heads + p.n_kv_heads;
+    int kv_head = is_q ? 0 : is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
+    float *b = buf[warp];
+
+    if (is_q || is_k) {
+        float ss = 0.0f;
+        for (int j = lane; j < hd; j += 32) {
+            float v = to_float(row[j]);
+            b[j] = v;
+            ss += v * v;
+        }
+        const float *w = is_q ? p.q_norm : p.k_norm;
+        if (w) {
+            ss = warp_sum(ss);
+            float scale = 1.0f / sqrtf(ss / (float)hd + p.eps);
+            for (int j = lane; j < hd; j += 32) b[j] = w[j] * (b[j] * scale);
+        }
+        __syncwarp();
+        if (p.cos) {
+            int half = p.rotary_dim / 2;
+            const float *c = p.cos + (long long)pos * half, *s = p.sin + (long long)pos * half;
+            for (int i = lane; i < half; i += 32) {
+                int ia = p.interleaved ? 2 * i : i, ib = p.interleaved ? 2 * i + 1 : i + half;
+                float a = b[ia], bb = b[ib];
+                b[ia] = a * c[i] - bb * s[i];
+                b[ib] = bb * c[i] + a * s[i];
+            }
+            __syncwarp();
+        }
+        for (int j = lane; j < hd; j += 32) row[j] = from_float<T>(b[j]);
+    }
+    if (is_q || !p.k_pool) return;
+    // A windowed cache keeps ring_pages pages; of the positions that share a place only the last is written.
+    if (p.cache.ring_pages > 0 &&
+        pos + p.cache.ring_pages * p.cache.tokens_per_page <= p.seq_len_after[seq] - 1)
+        return;
+    int page = cache_page(p.cache, p.seq_slot[seq], pos);
+    T *dst = (T *)(is_k ? p.k_pool : p.v_pool) + cache_offset(p.cache, page, kv_head, p.n_kv_heads, pos, hd);
+    if (is_k)
+        for (int j = lane; j < hd; j += 32) dst[j] = from_float<T>(b[j]);
+    else
+        for (int j = lane; j < hd; j += 32) dst[j] = row[j];
+}
+
+extern "C" int abk_qkv_prep(void *qkv, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int q_only,
+                            const int *token_seq, const int *token_pos, const int *seq_slot, const int *seq_len_after,
+                            const float *q_norm, const float *k_norm, float eps, const float *cos, const float *sin,
+                            int rotary_dim, int interleaved, void *k_pool, void *v_pool, const int *page_table,
+                            int table_width, int ring_pages, int tokens_per_page, void *stream) {
+    if (n_tokens <= 0) return 0;
+    if (head_dim > MAX_HEAD_DIM || head_dim < 2 || head_dim % 2)
+        ABK_REFUSE("qkv_prep: head_dim %d is not an even number up to %d", head_dim, MAX_HEAD_DIM);
+    if (cos && (rotary_dim < 2 || rotary_dim % 2 || rotary_dim > head_dim))
+        ABK_REFUSE("qkv_prep: rotary_dim %d does not fit head_dim %d", rotary_dim, head_dim);
+    QkvPrep p;
+    p.qkv = qkv, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads, p.head_dim = head_dim, p.q_only = q_only;
+    p.token_seq = token_seq, p.token_pos = token_pos, p.seq_slot = seq_slot, p.seq_len_after = seq_len_after;
+    p.q_norm = q_norm, p.k_norm = k_norm, p.eps = eps, p.cos = cos, p.sin = sin;
+    p.rotary_dim = rotary_dim, p.interleaved = interleaved, p.k_pool = k_pool, p.v_pool = v_pool;
+    p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = ring_pages;
+    p.cache.tokens_per_page = tokens_per_page;
+    int total_heads = n_heads + 2 * n_kv_heads;
+    dim3 grid(n_tokens, (total_heads + PREP_WARPS - 1) / PREP_WARPS);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == ABK_BF16)
+        qkv_prep_kernel<__nv_bfloat16><<<grid, PREP_WARPS * 32, 0, s>>>(p);
+    else
+        qkv_prep_kernel<float><<<grid, PREP_WARPS * 32, 0, s>>>(p);
+    return ABK_LAUNCH_RESULT();
+}

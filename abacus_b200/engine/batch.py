@@ -1,0 +1,93 @@
+"""The rows of one step, as the kernels see them.
+
+A step carries, for each sequence, its next tokens (a whole prompt, or one
+token), flattened into rows. Token-parallel kernels see only the rows; the
+attention kernels and the cache write also read which sequence and position a
+row belongs to. All index arrays of a step live in one int32 buffer, filled on
+the host and sent to the device in one copy.
+
+Rows beyond the step's tokens (padding up to a fixed size, for a captured
+graph) carry sequence index -1; kernels skip them and no result depends on them.
+"""
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+
+@dataclass
+class Sequence:
+    """One sequence's share of a step."""
+    slot: int
+    tokens: list  # its next tokens
+    start: int  # how many tokens the slot already holds
+    want: list  # places among `tokens` whose logits are wanted
+
+
+class StepBatch:
+    """Device-side index arrays of a step, with room for n_rows rows and n_seqs sequences."""
+
+    def __init__(self, n_rows, n_seqs, n_logit_rows, device):
+        self.device = torch.device(device)
+        self.cap_rows, self.cap_seqs, self.cap_logits = n_rows, n_seqs, max(1, n_logit_rows)
+        sizes = [n_rows, n_rows, n_rows, n_seqs, n_seqs + 1, n_seqs, n_seqs, self.cap_logits]
+        offsets = np.concatenate([[0], np.cumsum([-(-s // 4) * 4 for s in sizes])])  # 16-byte aligned parts
+        self._host = torch.zeros(int(offsets[-1]), dtype=torch.int32)
+        if self.device.type == "cuda":
+            self._host = self._host.pin_memory()
+        self._dev = torch.zeros(int(offsets[-1]), dtype=torch.int32, device=self.device)
+        names = ["tokens", "token_seq", "token_pos", "seq_slot", "seq_start", "seq_pos0", "seq_len_after", "logit_rows"]
+        self._h = {}
+        for name, off, size in zip(names, offsets[:-1], sizes):
+            self._h[name] = self._host[int(off):int(off) + size].numpy()
+            setattr(self, name, self._dev[int(off):int(off) + size])
+        self.n_rows = n_rows
+        self.n_tokens = self.n_seqs = self.n_logit_rows = 0
+        self.max_position = 0
+        self.max_len_after = 0
+        self.is_decode = False
+        self.any_continuation = False
+        self._sent = None
+
+    def fill(self, sequences):
+        """Write the step described by `sequences` (list of Sequence) and send it to the device."""
+        h = self._h
+        if self._sent is not None:
+            self._sent.synchronize()  # the last copy must have read the host buffer before it is rewritten
+        n_tokens = sum(len(s.tokens) for s in sequences)
+        n_logits = sum(len(s.want) for s in sequences)
+        if n_tokens > self.cap_rows or len(sequences) > self.cap_seqs or n_logits > self.cap_logits:
+            raise ValueError("step is larger than this StepBatch")
+        h["token_seq"][:] = -1
+        h["tokens"][:] = 0
+        h["token_pos"][:] = 0
+        h["seq_slot"][:] = 0
+        h["seq_pos0"][:] = 0
+        h["seq_len_after"][:] = 0
+        row, lr = 0, 0
+        for i, s in enumerate(sequences):
+            n = len(s.tokens)
+            h["tokens"][row:row + n] = s.tokens
+            h["token_seq"][row:row + n] = i
+            h["token_pos"][row:row + n] = np.arange(s.start, s.start + n)
+            h["seq_slot"][i] = s.slot
+            h["seq_start"][i] = row
+            h["seq_pos0"][i] = s.start
+            h["seq_len_after"][i] = s.start + n
+            for wpos in s.want:
+                if not 0 <= wpos < n:
+                    raise ValueError(f"wanted place {wpos} is outside the {n} tokens given")
+                h["logit_rows"][lr] = row + wpos
+                lr += 1
+            row += n
+        h["seq_start"][len(sequences):] = row
+        self.n_tokens, self.n_seqs, self.n_logit_rows = n_tokens, len(sequences), n_logits
+        self.max_position = max((s.start + len(s.tokens) - 1 for s in sequences), default=0)
+        self.max_len_after = self.max_position + 1
+        self.is_decode = all(len(s.tokens) == 1 for s in sequences)
+        self.any_continuation = any(s.start > 0 for s in sequences)
+        self._dev.copy_(self._host, non_blocking=True)
+        if self.device.type == "cuda":
+            self._sent = torch.cuda.Event()
+            self._sent.record()
+        return self

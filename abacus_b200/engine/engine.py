@@ -1,0 +1,109 @@
+"""The step function: a batch of sequences, their next tokens, the logits at the wanted places.
+
+An Engine holds a model, its cache and the slots of the live sequences. A step
+runs only the tokens it is given, as one batch, against what earlier steps left
+in the cache: whole prompts of unequal lengths in one step, then one token per
+sequence. This is abacus's forward(tokens, n, pos, logits, n_logits)
+(src/model.c:315-327) for a batch of sequences instead of one.
+"""
+import os
+
+import torch
+
+from ..cache import SequenceCache
+from ..config.registry import load_config
+from ..models.model import Model
+from ..weights.loader import load_folder
+from .batch import Sequence, StepBatch
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+          "f32": torch.float32}
+
+
+class StepError(ValueError):
+    """A step that asks for what cannot be run (context full, unknown slot, no tokens)."""
+
+
+def _device():
+    if not torch.cuda.is_available():
+        raise RuntimeError("abacus_b200 runs on a CUDA GPU (sm_100a); none is visible and there is no CPU path")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+def load_model(folder, dtype="bfloat16", device=None):
+    """A Model from a folder with config.json and *.safetensors; the class is chosen by config.json."""
+    dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
+    arch, config = load_config(folder)
+    spec = config.to_spec()
+    layout = arch.layout(spec)
+    tensors = load_folder(folder, lambda available: arch.tensor_names(spec, available))
+    model = Model(spec, layout, tensors, dtype, device or _device())
+    model.config = config
+    model.folder = os.path.abspath(folder)
+    return model
+
+
+class Engine:
+    def __init__(self, model, max_tokens, max_slots=None, max_context=None):
+        self.model = model
+        spec = model.spec
+        context = min(max_context or spec.max_positions, spec.max_positions)
+        self.cache = SequenceCache(model.cache_needs(), model.cache_sources(), max_tokens, model.ctx.dtype,
+                                   model.ctx.device, max_slots=max_slots, max_context=context)
+        self.max_context = self.cache.max_context
+        model.prepare(self.max_context)
+        self.vocab = spec.vocab
+
+    # ------------------------------------------------------------ sequences
+    def open(self):
+        """A slot for a new sequence."""
+        return self.cache.open_slot()
+
+    def close(self, slot):
+        """The sequence is finished: what it holds is given back."""
+        self.cache.close_slot(slot)
+
+    def length(self, slot):
+        return self.cache.length[slot]
+
+    # ------------------------------------------------------------ the step
+    def plan(self, entries):
+        """entries: [(slot, tokens, want)] -> [Sequence]; checks them and makes room in the cache."""
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        seqs, seen = [], set()
+        for slot, tokens, want in entries:
+            if slot not in self.cache.length:
+                raise StepError(f"slot {slot} is not open")
+            if slot in seen:
+                raise StepError(f"slot {slot} appears twice in one step")
+            seen.add(slot)
+            tokens = [int(t) for t in tokens]
+            if not tokens:
+                raise StepError(f"slot {slot}: a step must bring at least one token")
+            bad = [t for t in tokens if not 0 <= t < self.vocab]
+            if bad:
+                raise StepError(f"slot {slot}: token {bad[0]} is outside the vocabulary of {self.vocab}")
+            seqs.append(Sequence(slot, tokens, self.cache.length[slot], [int(w) for w in want]))
+        for s in seqs:
+            self.cache.reserve(s.slot, s.start + len(s.tokens))
+        return seqs
+
+    def step(self, entries):
+        """Run one step; returns float32 logits [wanted rows, vocab] on the device, in the order of
+        the entries and of each entry's `want`."""
+        seqs = self.plan(entries)
+        n_rows = sum(len(s.tokens) for s in seqs)
+        batch = StepBatch(n_rows, len(seqs), sum(len(s.want) for s in seqs), self.model.ctx.device).fill(seqs)
+        logits = self.model.forward(batch, self.cache)
+        self.last_batch = batch
+        for s in seqs:
+            self.cache.advance(s.slot, len(s.tokens))
+        return logits
+
+    def check_status(self):
+        """Raise if a kernel reported a fault (a bounded wait that ran out, a token out of range)."""
+        status = self.model.status.tolist()
+        if any(status):
+            self.model.status.zero_()
+            raise RuntimeError(f"a kernel reported a fault: status words {status}")

@@ -1,0 +1,144 @@
+"""The generation loop: batches of unequal prompts, stop tokens, sequences that end earlier, and as
+many batches one after another as there are requests.
+
+One request is abacus's chat loop (src/main.c:171-182): prefill, then sample,
+stop on a stop token (it is neither kept nor fed back), else keep the token and
+run it. The decisions of the loop (who is in which batch, who goes on, who is
+finished and why) are plain Python on the host, apart from the engine, so they
+are tested without a GPU.
+"""
+from dataclasses import dataclass, field
+
+import torch
+
+from ..cache.kv import TOKENS_PER_PAGE
+
+
+@dataclass
+class Request:
+    index: int
+    prompt: list
+    max_new_tokens: int
+    output: list = field(default_factory=list)
+    finish_reason: str = ""  # "stop", "length" or "context"
+    slot: int = -1
+
+
+def pages(n):
+    return -(-n // TOKENS_PER_PAGE)
+
+
+def plan_batches(requests, max_tokens, max_slots, max_context, batch_size=None):
+    """Cut the requests, in order, into batches that fit the cache.
+
+    A request may grow to min(prompt + max_new_tokens, max_context) tokens; a batch holds requests
+    while their pages fit max_tokens and their number fits max_slots (and batch_size, if given).
+    """
+    limit = min(max_slots, batch_size or max_slots)
+    batches, current, used = [], [], 0
+    for r in requests:
+        if not r.prompt:
+            raise ValueError(f"request {r.index} has an empty prompt")
+        if len(r.prompt) > max_context:
+            raise ValueError(f"request {r.index}: prompt of {len(r.prompt)} tokens is longer than the context "
+                             f"of {max_context}")
+        need = pages(min(len(r.prompt) + r.max_new_tokens, max_context))
+        if need > pages(max_tokens):
+            raise ValueError(f"request {r.index} needs {need * TOKENS_PER_PAGE} tokens of cache; "
+                             f"the cache has {max_tokens}")
+        if current and (len(current) >= limit or used + need > pages(max_tokens)):
+            batches.append(current)
+            current, used = [], 0
+        current.append(r)
+        used += need
+    if current:
+        batches.append(current)
+    return batches
+
+
+class LiveBatch:
+    """The requests of one batch that are still running, and what happens to each sampled token."""
+
+    def __init__(self, requests, stop_tokens, max_context):
+        self.live = list(requests)
+        self.stop_tokens = frozenset(stop_tokens)
+        self.max_context = max_context
+
+    def first_step(self):
+        """The prefill: every prompt whole, logits wanted at its last token."""
+        return [(r.slot, r.prompt, [len(r.prompt) - 1]) for r in self.live]
+
+    def take(self, sampled):
+        """sampled[i] is the token drawn for self.live[i]. Returns (finished requests, next step's
+        entries): a request ends on a stop token (not kept), after max_new_tokens, or when its
+        context is full (src/main.c:174-176)."""
+        finished, entries, still = [], [], []
+        for r, token in zip(self.live, sampled):
+            token = int(token)
+            if r.max_new_tokens <= 0:
+                r.finish_reason = "length"
+            elif token in self.stop_tokens:
+                r.finish_reason = "stop"
+            else:
+                r.output.append(token)
+                if len(r.output) >= r.max_new_tokens:
+                    r.finish_reason = "length"
+                elif len(r.prompt) + len(r.output) >= self.max_context:
+                    r.finish_reason = "context"
+            if r.finish_reason:
+                finished.append(r)
+            else:
+                still.append(r)
+                entries.append((r.slot, [token], [0]))
+        self.live = still
+        return finished, entries
+
+
+class Generator:
+    """Runs requests through an engine. `engine` needs open(), close(slot), step(entries) -> logits,
+    max_context and a cache with n_pages and max_slots; `sampler` needs states() and sample()."""
+
+    def __init__(self, engine, sampler, stop_tokens=()):
+        self.engine, self.sampler, self.stop_tokens = engine, sampler, tuple(stop_tokens)
+        self.stats = {"prefill_steps": 0, "decode_steps": 0, "batches": 0}
+        self.rng = None
+
+    def generate(self, prompts, max_new_tokens, batch_size=None):
+        """prompts: list of token-id lists. Returns the Request objects, outputs filled, in order."""
+        requests = [Request(i, [int(t) for t in p], max_new_tokens) for i, p in enumerate(prompts)]
+        cache = self.engine.cache
+        for batch in plan_batches(requests, cache.n_pages * TOKENS_PER_PAGE, cache.max_slots,
+                                  self.engine.max_context, batch_size):
+            self.run_batch(batch)
+            self.stats["batches"] += 1
+        return requests
+
+    def run_batch(self, batch):
+        engine = self.engine
+        for r in batch:
+            r.slot = engine.open()
+        live = LiveBatch(batch, self.stop_tokens, engine.max_context)
+        # one random stream per request, kept at the request's slot
+        if self.rng is None:
+            self.rng = torch.zeros(engine.cache.max_slots, dtype=torch.int64, device=self.sampler.device)
+        slots = torch.tensor([r.slot for r in batch], dtype=torch.int64, device=self.sampler.device)
+        self.rng.index_copy_(0, slots, self.sampler.states([r.index for r in batch]))
+        try:
+            entries = live.first_step()
+            self.stats["prefill_steps"] += 1
+            while entries:
+                logits = engine.step(entries)
+                sampled = self.sampler.sample(logits, self.rng, index=engine.last_batch.seq_slot).tolist()
+                finished, entries = live.take(sampled)
+                for r in finished:
+                    engine.close(r.slot)
+                    r.slot = -1
+                if entries:
+                    self.stats["decode_steps"] += 1
+        finally:
+            for r in batch:
+                if r.slot >= 0:
+                    engine.close(r.slot)
+                    r.slot = -1
+        if hasattr(engine, "check_status"):
+            engine.check_status()

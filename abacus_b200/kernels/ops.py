@@ -1,0 +1,200 @@
+"""Python faces of the CUDA kernels: they check their arguments and launch on torch's current stream.
+
+Every function here runs a hand-written kernel from csrc/; none has a CPU or
+library fallback. Tensors must live on the GPU and be contiguous where a kernel
+assumes it; a kernel that does not take a size raises KernelRefused with the
+reason instead of computing something else.
+"""
+import ctypes
+
+import torch
+
+from .build import load_module
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class KernelRefused(KernelError):
+    """The sizes or types given are outside what the kernel is built for."""
+
+
+def _dt(t):
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {t.dtype} is neither float32 nor bfloat16")
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("a kernel was given a tensor that is not on the GPU; there is no CPU path")
+
+
+def _check(lib, rc, what):
+    if rc == 0:
+        return
+    if rc < 0:
+        raise KernelRefused(lib.abk_last_error().decode())
+    raise KernelError(f"{what}: CUDA error {rc} at launch")
+
+
+_i, _ll, _f = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+def embed(tokens, table, x, status):
+    """x[t] = float(table[tokens[t]]) (src/model.c:290-291). tokens int32 [T], x float32 [T, d]."""
+    _need_cuda(tokens, table, x, status)
+    lib = load_module("elementwise")
+    n, d = x.shape
+    assert tokens.dtype == torch.int32 and x.dtype == torch.float32 and tokens.numel() >= n
+    assert table.is_contiguous() and x.is_contiguous() and table.shape[1] == d
+    _check(lib, lib.abk_embed(_p(tokens), _p(table), _i(_dt(table)), _p(x), _i(n), _i(d), _i(table.shape[0]),
+                              _p(status), _stream()), "embed")
+
+
+def add_rmsnorm(x, y, weight, out, eps, rows=None, n_rows=None):
+    """x += y (if given); out = weight * x / sqrt(mean(x^2) + eps) (src/model.c:238-244).
+
+    rows (int32) picks the rows of x that are normed into out[0:len(rows)]; x is then left unchanged.
+    """
+    _need_cuda(x, y, weight, out, rows)
+    lib = load_module("elementwise")
+    d = x.shape[-1]
+    n = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == d
+    assert y is None or (y.dtype == torch.float32 and y.shape == x.shape and y.is_contiguous())
+    assert x.is_contiguous() and out.is_contiguous() and out.shape[-1] == d and out.shape[0] >= n
+    _check(lib, lib.abk_add_rmsnorm(_p(x), _p(y), _p(weight), _p(out), _i(_dt(out)), _p(rows), _i(n), _i(d),
+                                    _f(eps), _stream()), "add_rmsnorm")
+
+
+def swiglu(gate_up, act):
+    """act = silu(gate) * up for rows laid out [gate | up] (src/model.c:274-282)."""
+    _need_cuda(gate_up, act)
+    lib = load_module("elementwise")
+    n, two_i = gate_up.shape
+    assert act.shape == (n, two_i // 2) and act.dtype == gate_up.dtype
+    assert gate_up.is_contiguous() and act.is_contiguous()
+    _check(lib, lib.abk_swiglu(_p(gate_up), _p(act), _i(_dt(act)), _i(n), _i(two_i // 2), _stream()), "swiglu")
+
+
+def qkv_prep(qkv, n_heads, n_kv_heads, head_dim, batch, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved,
+             cache, q_only=False):
+    """Per-head norm of q and k, rotary encoding, and the cache write of k and v (src/model.c:247-259).
+
+    qkv [T, (Hq + 2 Hkv) * hd] is changed in place. batch: engine.batch.StepBatch. cache: a
+    cache.LayerKV or None (nothing written). q_only: only the q heads are prepared.
+    """
+    _need_cuda(qkv, q_norm, k_norm, cos, sin)
+    lib = load_module("elementwise")
+    n = batch.n_rows
+    assert qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim and qkv.shape[0] >= n
+    if cos is not None:
+        assert cos.dtype == torch.float32 and cos.shape == sin.shape and cos.shape[1] == rotary_dim // 2
+        if batch.max_position >= cos.shape[0]:
+            raise KernelError(f"position {batch.max_position} is beyond the rotary table of {cos.shape[0]} positions")
+    if cache is not None:
+        assert cache.k.dtype == qkv.dtype and cache.k.shape[1:] == (n_kv_heads, cache.tokens_per_page, head_dim)
+    _check(lib, lib.abk_qkv_prep(
+        _p(qkv), _i(_dt(qkv)), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(1 if q_only else 0),
+        _p(batch.token_seq),
+        _p(batch.token_pos), _p(batch.seq_slot), _p(batch.seq_len_after), _p(q_norm), _p(k_norm), _f(eps or 0.0),
+        _p(cos), _p(sin), _i(rotary_dim), _i(1 if interleaved else 0),
+        _p(cache.k if cache is not None else None), _p(cache.v if cache is not None else None),
+        _p(cache.page_table if cache is not None else None), _i(cache.table_width if cache is not None else 0),
+        _i(cache.ring_pages if cache is not None else 0), _i(cache.tokens_per_page if cache is not None else 1),
+        _stream()), "qkv_prep")
+
+
+def attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False):
+    """Causal grouped-query attention of every token of the step (src/model.c:197-211).
+
+    q is read from qkv's q columns. Keys and values come from `cache` (a cache.LayerView), or, with
+    from_step, from this step's own rows of qkv (only right when every sequence starts at position 0).
+    """
+    _need_cuda(qkv, out)
+    lib = load_module("attention_generic")
+    n = batch.n_rows
+    row = (n_heads + 2 * n_kv_heads) * head_dim
+    assert qkv.is_contiguous() and qkv.shape[1] == row and out.is_contiguous() and out.dtype == qkv.dtype
+    assert out.shape[1] == n_heads * head_dim and out.shape[0] >= n and qkv.shape[0] >= n
+    esize = qkv.element_size()
+    k_step = ctypes.c_void_p(qkv.data_ptr() + n_heads * head_dim * esize) if from_step else ctypes.c_void_p(0)
+    v_step = ctypes.c_void_p(qkv.data_ptr() + (n_heads + n_kv_heads) * head_dim * esize) if from_step else ctypes.c_void_p(0)
+    if not from_step:
+        assert cache is not None and cache.k.dtype == qkv.dtype
+    _check(lib, lib.abk_attention_generic(
+        _p(qkv), _ll(row), _p(out), _i(_dt(qkv)), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale),
+        _i(window or 0), _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(batch.seq_start),
+        _p(batch.seq_pos0), _p(cache.k if cache is not None else None), _p(cache.v if cache is not None else None),
+        _p(cache.page_table if cache is not None else None), _i(cache.table_width if cache is not None else 0),
+        _i(cache.ring_pages if cache is not None else 0), _i(cache.tokens_per_page if cache is not None else 1),
+        k_step, v_step, _ll(row), _stream()), "attention")
+
+
+def gemm_simt(x, w, out, m=None):
+    """out[:m] = x[:m] . w^T on the CUDA cores in float32, any sizes (src/model.c:299 and the like)."""
+    _need_cuda(x, w, out)
+    lib = load_module("gemm_simt")
+    m = x.shape[0] if m is None else m
+    n, k = w.shape
+    assert x.shape[1] == k and out.shape[1] == n and x.shape[0] >= m and out.shape[0] >= m
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(lib, lib.abk_gemm_simt(_p(x), _i(_dt(x)), _p(w), _i(_dt(w)), _p(out), _i(_dt(out)), _i(m), _i(n), _i(k),
+                                  _ll(x.stride(0)), _ll(w.stride(0)), _ll(out.stride(0)), _stream()), "gemm_simt")
+
+
+def argmax(logits, out, n_rows=None):
+    """out[r] = index of the first maximum of logits[r] (src/main.c:31-36)."""
+    _need_cuda(logits, out)
+    lib = load_module("sampling")
+    n = logits.shape[0] if n_rows is None else n_rows
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32 and out.numel() >= n
+    _check(lib, lib.abk_argmax(_p(logits), _ll(logits.stride(0)), _i(n), _i(logits.shape[1]), _p(out), _stream()),
+           "argmax")
+
+
+def sample_topk(logits, temperature, top_k, rng_state, out, n_rows=None, rng_index=None):
+    """Draw from the top_k logits at a temperature (src/main.c:39-56).
+
+    rng_state int64 holds xorshift64 states; row r uses and advances rng_state[rng_index[r]]
+    (rng_state[r] without rng_index).
+    """
+    _need_cuda(logits, rng_state, out, rng_index)
+    lib = load_module("sampling")
+    n = logits.shape[0] if n_rows is None else n_rows
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    assert rng_state.dtype == torch.int64 and out.numel() >= n
+    assert rng_index is None or (rng_index.dtype == torch.int32 and rng_index.numel() >= n)
+    assert rng_index is not None or rng_state.numel() >= n
+    _check(lib, lib.abk_sample_topk(_p(logits), _ll(logits.stride(0)), _i(n), _i(logits.shape[1]), _f(temperature),
+                                    _i(top_k), _p(rng_state), _p(rng_index), _p(out), _stream()), "sample_topk")
+
+
+def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, ws=None):
+    """Attention of a step: picks the kernel for the phase and sizes; every case the faster kernels
+    do not take goes to the general one."""
+    attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=from_step)
+
+
+def gemm_tc_takes(x, w, out):
+    """Whether the tensor-core kernel takes this product (else the CUDA-core kernel runs it)."""
+    return False
+
+
+def gemm_tc(x, w, out, m=None):
+    raise KernelRefused("the tensor-core matrix product is not built for this shape")

@@ -1,0 +1,75 @@
+"""Grouped-query causal attention over the paged cache (src/model.c:197-211, 247-259).
+
+The mixer owns the q/k/v and output projections, the optional per-head norm of
+q and k, and a position encoding; its sizes, scale, eps and window come from
+its spec. q, k and v are one stacked matrix, as in src/model.c:88-93.
+"""
+import torch
+
+from ..cache.need import CacheNeed
+from ..kernels import ops
+from .base import MIXERS, POSITIONS, to_device
+from .linear import Linear
+
+
+@MIXERS.register("attention")
+class Attention:
+    def __init__(self, spec):
+        s = self.spec = spec
+        if s.n_heads % s.n_kv_heads:
+            raise ValueError(f"{s.n_heads} query heads do not divide into {s.n_kv_heads} kv heads")
+        if s.head_dim % 8 or s.head_dim > 256:
+            raise ValueError(f"head_dim {s.head_dim}: the attention kernels take multiples of 8 up to 256")
+        self.position = POSITIONS.build(s.position) if s.position is not None else None
+        self.q_size, self.kv_size = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
+        self.cos = self.sin = None
+
+    def param_shapes(self):
+        s = self.spec
+        shapes = {"wq": (self.q_size, s.hidden), "wk": (self.kv_size, s.hidden), "wv": (self.kv_size, s.hidden),
+                  "wo": (s.hidden, self.q_size)}
+        if s.qk_norm_eps is not None:
+            shapes.update(q_norm=(s.head_dim,), k_norm=(s.head_dim,))
+        return shapes
+
+    def bind(self, params, ctx):
+        self.ctx = ctx
+        wqkv = torch.cat([params["wq"], params["wk"], params["wv"]], dim=0)
+        self.qkv_proj = Linear(to_device(wqkv, ctx, ctx.dtype))
+        self.q_proj = Linear(self.qkv_proj.weight[:self.q_size])  # for entries that read another entry's cache
+        self.o_proj = Linear(to_device(params["wo"], ctx, ctx.dtype))
+        self.q_norm = to_device(params["q_norm"], ctx, torch.float32) if "q_norm" in params else None
+        self.k_norm = to_device(params["k_norm"], ctx, torch.float32) if "k_norm" in params else None
+
+    def cache_need(self):
+        s = self.spec
+        return CacheNeed(n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window)
+
+    def prepare(self, max_positions, device):
+        if self.position is not None:
+            self.cos, self.sin = self.position.tables(max_positions, device)
+
+    def forward(self, xn, out, batch, cache, ws):
+        s = self.spec
+        n = batch.n_rows
+        qkv = ws.get("qkv", (n, self.q_size + 2 * self.kv_size), self.ctx.dtype)
+        att = ws.get("att", (n, self.q_size), self.ctx.dtype)
+        writes = cache.owns_storage
+        if writes:
+            self.qkv_proj.forward(xn, qkv, n)
+        else:  # keys and values are another entry's: only q is needed
+            self.q_proj.forward(xn, qkv[:, :self.q_size], n)
+        ops.qkv_prep(qkv, s.n_heads, s.n_kv_heads, s.head_dim, batch, self.q_norm, self.k_norm, s.qk_norm_eps,
+                     self.cos, self.sin, self.position.rotary_dim if self.position else 0,
+                     self.position.interleaved if self.position else False, cache.kv if writes else None,
+                     q_only=not writes)
+        # A windowed cache keeps only the last keys; a prompt longer than that reads its keys from
+        # this step's own rows, which hold all of them when the sequences start at position 0.
+        from_step = s.window is not None and not batch.is_decode
+        if from_step and (batch.any_continuation or not writes):
+            raise ops.KernelRefused("windowed attention takes several tokens of a sequence only at its start, "
+                                    "and only with keys of its own")
+        ops.attention(qkv, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, batch, cache.kv,
+                      from_step=from_step, ws=ws)
+        self.o_proj.forward(att, out, n)
+        return out

@@ -1,0 +1,22 @@
+"""out = x . W^T, the matrix product every projection is (src/model.c:299, 302, 307, 309, 324).
+
+float32: CUDA-core kernel with a fixed summation order. bfloat16: the tcgen05
+tensor-core kernel where it takes the shape, else the CUDA-core kernel.
+"""
+import torch
+
+from ..kernels import ops
+
+
+class Linear:
+    def __init__(self, weight):
+        assert weight.dim() == 2 and weight.is_contiguous()
+        self.weight = weight
+        self.out_features, self.in_features = weight.shape
+
+    def forward(self, x, out, m=None):
+        if self.weight.dtype == torch.bfloat16 and ops.gemm_tc_takes(x, self.weight, out):
+            ops.gemm_tc(x, self.weight, out, m)
+        else:
+            ops.gemm_simt(x, self.weight, out, m)
+        return out

@@ -1,0 +1,121 @@
+"""The plain implementation against abacus's own engine, and against itself."""
+import hashlib
+import json
+import os
+
+import numpy as np
+
+from helpers import TINY, log_softmax64, make_model_folder
+from plain import qwen3_plain as plain
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def test_plain_matches_abacus_engine(tmp_path):
+    """abacus's engine is int8 (tests/golden/make_golden.py), so its own rule for quantised weights
+    applies (tools/check.py:24, 94-97): the same top token at >= 90 % of the positions and a mean KL
+    <= 0.02. (Seen here: 100 %, KL 8.6e-4, mean abs difference 0.03 on logits of std 1.3.)"""
+    meta = json.load(open(os.path.join(GOLDEN, "tinyA_abacus.json")))
+    golden = np.load(os.path.join(GOLDEN, "tinyA_abacus.npy"))
+    folder = make_model_folder(tmp_path, "A")
+    digest = hashlib.sha256(open(os.path.join(folder, "model.safetensors"), "rb").read()).hexdigest()
+    assert digest == meta["weights_sha256"], "the random weights are not the ones the golden logits were made with"
+    cfg, w = plain.load(folder)
+    got = plain.forward(cfg, w, meta["ids"])
+    assert got.shape == golden.shape
+    agreement = (got.argmax(-1) == golden.argmax(-1)).mean()
+    lp, lq = log_softmax64(got), log_softmax64(golden)
+    kl = (np.exp(lp) * (lp - lq)).sum(-1).mean()
+    assert agreement >= 0.90 and kl <= 0.02, (agreement, kl)
+
+
+def test_causality_and_prefix_invariance(tmp_path):
+    """Logits at a position depend only on the tokens up to it."""
+    folder = make_model_folder(tmp_path, "C")
+    cfg, w = plain.load(folder)
+    rng = np.random.default_rng(0)
+    ids = [int(t) for t in rng.integers(0, cfg["vocab"], 40)]
+    whole = plain.forward(cfg, w, ids)
+    part = plain.forward(cfg, w, ids[:29])
+    np.testing.assert_allclose(whole[:29], part, atol=2e-6)
+    other = plain.forward(cfg, w, ids[:29] + [int(t) for t in rng.integers(0, cfg["vocab"], 11)])
+    np.testing.assert_allclose(whole[:29], other[:29], atol=2e-6)
+
+
+def test_window_limits_what_is_seen(tmp_path):
+    """With a window of W a change of a token W or more places back leaves a windowed-only model's
+    logits as they were; configuration C mixes full and windowed layers, so here the parts are checked."""
+    rng = np.random.default_rng(1)
+    n, hq, hkv, hd, win = 50, 4, 2, 16, 7
+    q = rng.standard_normal((n, hq, hd)).astype(np.float32)
+    k = rng.standard_normal((n, hkv, hd)).astype(np.float32)
+    v = rng.standard_normal((n, hkv, hd)).astype(np.float32)
+    full = plain.attention(q, k, v)
+    windowed = plain.attention(q, k, v, window=win)
+    np.testing.assert_allclose(full[:win], windowed[:win], atol=1e-6)  # the first W tokens see everything
+    k2, v2 = k.copy(), v.copy()
+    k2[10], v2[10] = 9.0, -9.0
+    changed = plain.attention(q, k2, v2, window=win)
+    same = [i for i in range(n) if not (10 <= i <= 10 + win - 1)]
+    np.testing.assert_allclose(changed[same], windowed[same], atol=1e-6)
+    assert np.abs(changed[10 + win - 1] - windowed[10 + win - 1]).max() > 1e-3  # the window's far edge is inside
+
+
+def test_rope_is_a_rotation_and_position_zero_is_identity():
+    cos, sin = plain.rope_table(9, 16, 10000.0)
+    x = np.random.default_rng(2).standard_normal((9, 3, 16)).astype(np.float32)
+    y = plain.rope(x, cos, sin)
+    np.testing.assert_allclose(y[0], x[0], atol=0)
+    np.testing.assert_allclose(np.linalg.norm(y, axis=-1), np.linalg.norm(x, axis=-1), rtol=1e-5)
+    # pair (i, i + 8) turns by pos * theta^(-2i/16) (src/model.c:121, 173-181)
+    ang = np.arctan2(y[5, 0, 8], y[5, 0, 0]) - np.arctan2(x[5, 0, 8], x[5, 0, 0])
+    assert abs((ang - 5.0 + np.pi) % (2 * np.pi) - np.pi) < 1e-4
+
+
+def test_rmsnorm_swiglu_softmax():
+    x = np.array([[3.0, 4.0]], dtype=np.float32)
+    np.testing.assert_allclose(plain.rmsnorm(x, np.array([2.0, 0.5], dtype=np.float32), 0.0),
+                               [[2 * 3 / np.sqrt(12.5), 0.5 * 4 / np.sqrt(12.5)]], rtol=1e-6)
+    gu = np.array([[0.0, 1.0, 5.0, 7.0]], dtype=np.float32)
+    np.testing.assert_allclose(plain.swiglu(gu), [[0.0, 7.0 / (1 + np.exp(-1.0))]], rtol=1e-6)
+    p = plain.softmax(np.array([1000.0, 1000.0], dtype=np.float32))
+    np.testing.assert_allclose(p, [0.5, 0.5])
+
+
+def test_sampler_follows_abacus():
+    """Greedy takes the first maximum; at a temperature the draw is among the 20 largest, and the
+    xorshift64 state advances once per token (src/main.c:31-56)."""
+    logits = np.array([0.1, 2.0, 2.0, -1.0], dtype=np.float32)
+    assert plain.argmax(logits) == 1
+    assert plain.sample(logits, 0.0, 5)[0] == 1
+    rng = np.random.default_rng(3)
+    big = rng.standard_normal(500).astype(np.float32)
+    top20 = set(np.argsort(-big, kind="stable")[:20].tolist())
+    state, seen = 12345, set()
+    for _ in range(300):
+        tok, state = plain.sample(big, 1.5, state)
+        assert tok in top20
+        seen.add(tok)
+    assert len(seen) > 5
+    assert plain.xorshift64(1) == 1082269761  # 1 ^ 1<<13 = 8193; ^ >>7 = 8257; ^ <<17
+    assert plain.sample(big, 0.8, 0)[0] == int(np.argmax(big))  # a zero state stays zero: r = 0 takes the top
+
+
+def test_bf16_round_matches_export():
+    """tools/export.py:49-51: (u + 0x7FFF + ((u >> 16) & 1)) >> 16."""
+    a = np.array([1.0, 1.00390625, 1.005859375, -3.1415927, 1e-30], dtype=np.float32)
+    r = plain.bf16_round(a)
+    assert (r.view(np.uint32) & 0xFFFF == 0).all()
+    assert r[0] == 1.0 and r[1] == 1.0 and r[2] == np.float32(1.0078125)  # ties to even, then up
+
+
+def test_schedule_reuse_changes_result_and_is_consistent(tmp_path):
+    folder = make_model_folder(tmp_path, "A")
+    cfg, w = plain.load(folder)
+    ids = [3, 9, 200, 41, 7, 7, 100]
+    base = plain.forward(cfg, w, ids)
+    twice = plain.forward(cfg, w, ids, schedule=[(0, None), (1, None), (0, None)])
+    shared = plain.forward(cfg, w, ids, schedule=[(0, None), (1, 0)])
+    assert np.abs(base - twice).max() > 1e-3 and np.abs(base - shared).max() > 1e-3
+    explicit = plain.forward(cfg, w, ids, schedule=[(0, None), (1, None)])
+    np.testing.assert_array_equal(base, explicit)
