@@ -10,7 +10,7 @@ def __getattr__(name):
     if name in ("Engine", "load_model", "StepError"):
         from . import engine
         return getattr(engine, name)
-    if name in ("generate", "Generator", "Request"):
-        from .engine import generate as g
-        return getattr(g, name)
+    if name in ("LM", "generate"):
+        from . import api
+        return getattr(api, name)
     raise AttributeError(name)

@@ -82,6 +82,7 @@ class StepBatch:
             row += n
         h["seq_start"][len(sequences):] = row
         self.n_tokens, self.n_seqs, self.n_logit_rows = n_tokens, len(sequences), n_logits
+        self.sequences = list(sequences)  # host view, for mixers that walk the sequences themselves
         self.max_position = max((s.start + len(s.tokens) - 1 for s in sequences), default=0)
         self.max_len_after = self.max_position + 1
         self.is_decode = all(len(s.tokens) == 1 for s in sequences)

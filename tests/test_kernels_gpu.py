@@ -1,0 +1,278 @@
+"""Each kernel alone against its plain reference, at sizes the engine's tiny models do not use."""
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from abacus_b200.kernels import ops
+    return ops
+
+
+def dev(a, dtype=torch.float32):
+    return torch.tensor(np.asarray(a), dtype=dtype, device="cuda")
+
+
+def bf(a):
+    return plain.bf16_round(np.asarray(a, dtype=np.float32))
+
+
+def close(got, want, dtype):
+    got = got.float().cpu().numpy()
+    if dtype == torch.float32:
+        np.testing.assert_allclose(got, want, rtol=2e-5, atol=2e-6)
+    else:  # one bfloat16 rounding of the result: 2^-8 relative, plus float32 noise
+        np.testing.assert_allclose(got, want, rtol=2 ** -7, atol=1e-6)
+
+
+def test_embed(ops):
+    rng = np.random.default_rng(0)
+    table = bf(rng.standard_normal((1000, 72)))
+    tokens = rng.integers(0, 1000, 33)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    for tdtype in (torch.bfloat16, torch.float32):
+        x = torch.empty(33, 72, device="cuda")
+        ops.embed(dev(tokens, torch.int32), dev(table, tdtype), x, status)
+        np.testing.assert_array_equal(x.cpu().numpy(), plain.embed(tokens, table))
+    assert status.tolist() == [0, 0, 0, 0]
+    ops.embed(dev([5, 1000, 7], torch.int32), dev(table), torch.empty(3, 72, device="cuda"), status)
+    assert status[0].item() == 1  # a token outside the vocabulary is reported, not read
+
+
+@pytest.mark.parametrize("d", [200, 72, 1030, 4096])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(ops, d, out_dtype):
+    rng = np.random.default_rng(d)
+    x, y = rng.standard_normal((7, d)).astype(np.float32), rng.standard_normal((7, d)).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+    eps = 3e-5
+    xd, out = dev(x), torch.empty(7, d, dtype=out_dtype, device="cuda")
+    ops.add_rmsnorm(xd, dev(y), dev(w), out, eps)
+    np.testing.assert_array_equal(xd.cpu().numpy(), x + y)  # the residual stream is updated
+    close(out, plain.rmsnorm(x + y, w, eps), out_dtype)
+    xd = dev(x)
+    ops.add_rmsnorm(xd, None, dev(w), out, eps)
+    close(out, plain.rmsnorm(x, w, eps), out_dtype)
+    rows = [6, 0, 3, 3]
+    xd, out = dev(x), torch.empty(4, d, dtype=out_dtype, device="cuda")
+    ops.add_rmsnorm(xd, dev(y), dev(w), out, eps, rows=dev(rows, torch.int32))
+    close(out, plain.rmsnorm((x + y)[rows], w, eps), out_dtype)
+    np.testing.assert_array_equal(xd.cpu().numpy(), x)  # with rows, x is left alone
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(ops, dtype):
+    rng = np.random.default_rng(1)
+    gu = (3 * rng.standard_normal((9, 2 * 100))).astype(np.float32)
+    if dtype == torch.bfloat16:
+        gu = bf(gu)
+    act = torch.empty(9, 100, dtype=dtype, device="cuda")
+    ops.swiglu(dev(gu, dtype), act)
+    close(act, plain.swiglu(gu), dtype)
+
+
+@pytest.mark.parametrize("m, n, k", [(5, 37, 50), (1, 389, 96), (130, 70, 33), (64, 64, 16), (3, 1, 7)])
+def test_gemm_simt(ops, m, n, k):
+    rng = np.random.default_rng(m * n + k)
+    x, w = rng.standard_normal((m, k)).astype(np.float32), rng.standard_normal((n, k)).astype(np.float32)
+    out = torch.empty(m, n, device="cuda")
+    ops.gemm_simt(dev(x), dev(w), out)
+    np.testing.assert_allclose(out.cpu().numpy(), plain.linear(x, w), rtol=1e-5, atol=1e-5)
+    xb, wb = bf(x), bf(w)
+    for odt in (torch.float32, torch.bfloat16):
+        out = torch.empty(m, n, dtype=odt, device="cuda")
+        ops.gemm_simt(dev(xb, torch.bfloat16), dev(wb, torch.bfloat16), out)
+        close(out, plain.linear(xb, wb), odt) if odt == torch.bfloat16 else np.testing.assert_allclose(
+            out.cpu().numpy(), plain.linear(xb, wb), rtol=1e-5, atol=1e-5)
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch(ops):
+    """The float32 product sums over k in one fixed order: a row alone equals the row in a batch, bit for bit."""
+    rng = np.random.default_rng(5)
+    x, w = rng.standard_normal((77, 300)).astype(np.float32), rng.standard_normal((101, 300)).astype(np.float32)
+    whole = torch.empty(77, 101, device="cuda")
+    ops.gemm_simt(dev(x), dev(w), whole)
+    for r in (0, 63, 64, 76):
+        one = torch.empty(1, 101, device="cuda")
+        ops.gemm_simt(dev(x[r:r + 1]), dev(w), one)
+        assert torch.equal(one[0], whole[r])
+
+
+def test_argmax_takes_the_first_maximum(ops):
+    rng = np.random.default_rng(2)
+    logits = rng.standard_normal((6, 5003)).astype(np.float32)
+    logits[1, 4000] = logits[1, 77] = 9.0
+    logits[2, 5002] = 10.0
+    logits[3, :] = 0.5
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    ops.argmax(dev(logits), out)
+    assert out.tolist() == [plain.argmax(r) for r in logits]
+    assert out[1].item() == 77 and out[2].item() == 5002 and out[3].item() == 0
+
+
+@pytest.mark.parametrize("temp, top_k", [(0.8, 20), (1.7, 5), (0.3, 64)])
+def test_sample_topk_draws_what_the_plain_sampler_draws(ops, temp, top_k):
+    rng = np.random.default_rng(3)
+    vocab, rows = 2311, 16
+    logits = (2 * rng.standard_normal((rows, vocab))).astype(np.float32)
+    logits[4, 100] = logits[4, 50] = logits[4].max() + 1  # a tie at the top
+    logits[5, :] = 1.0  # all equal: the first top_k indices
+    states = [int(s) for s in rng.integers(1, 2 ** 62, rows)]
+    st = dev(states, torch.int64)
+    index = dev(list(range(rows))[::-1], torch.int32)  # row r uses state rows-1-r
+    ld, out = dev(logits), torch.empty(rows, dtype=torch.int32, device="cuda")
+    want_states = list(states)
+    for step in range(5):
+        ops.sample_topk(ld, temp, top_k, st, out, rng_index=index)
+        got = out.tolist()
+        for r in range(rows):
+            tok, want_states[rows - 1 - r] = plain.sample(logits[r], temp, want_states[rows - 1 - r], top_k)
+            assert got[r] == tok, (step, r)
+    assert st.tolist() == want_states
+    with pytest.raises(ops.KernelRefused):
+        ops.sample_topk(ld, temp, 65, st, out)
+    with pytest.raises(ops.KernelRefused):
+        ops.sample_topk(ld, 0.0, 5, st, out)
+
+
+# ------------------------------------------------------------------ q/k/v preparation and attention
+
+class Harness:
+    """A cache and steps for one attention layer, without a model around it."""
+
+    def __init__(self, hq, hkv, hd, dtype, window=None, max_tokens=64 * 24):
+        from abacus_b200.cache import CacheNeed, SequenceCache
+        self.hq, self.hkv, self.hd, self.dtype, self.window = hq, hkv, hd, dtype, window
+        self.cache = SequenceCache([CacheNeed(hkv, hd, window)], [None], max_tokens, dtype, "cuda", max_context=1024)
+
+    def step(self, ops, seqs, qkv, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved, scale, from_step=False):
+        """seqs: [(slot, n_new)]; qkv float32 numpy [rows, (hq + 2 hkv) * hd]. Returns attention output."""
+        from abacus_b200.engine.batch import Sequence, StepBatch
+        ss = []
+        for slot, n in seqs:
+            ss.append(Sequence(slot, [0] * n, self.cache.length[slot], []))
+            self.cache.reserve(slot, self.cache.length[slot] + n)
+        rows = sum(n for _, n in seqs)
+        batch = StepBatch(rows + 3, len(seqs) + 1, 0, "cuda").fill(ss)  # three padding rows at the end
+        pad = np.full((3, qkv.shape[1]), 7.0, dtype=np.float32)
+        q = dev(np.concatenate([qkv, pad]), self.dtype)
+        kv = self.cache.views[0].kv
+        ops.qkv_prep(q, self.hq, self.hkv, self.hd, batch, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved, kv)
+        out = torch.full((rows + 3, self.hq * self.hd), 5.0, dtype=self.dtype, device="cuda")
+        ops.attention_generic(q, out, self.hq, self.hkv, self.hd, scale, self.window, batch, kv, from_step=from_step)
+        for slot, n in seqs:
+            self.cache.advance(slot, n)
+        assert float(out[rows:].float().abs().sum()) == 0.0  # padding rows give zeros and disturb nothing
+        return q[:rows].float().cpu().numpy(), out[:rows].float().cpu().numpy()
+
+
+def plain_prep(qkv, hq, hkv, hd, qn, kn, eps, cos, sin, rotary_dim, interleaved, pos0):
+    n = qkv.shape[0]
+    q = qkv[:, :hq * hd].reshape(n, hq, hd)
+    k = qkv[:, hq * hd:(hq + hkv) * hd].reshape(n, hkv, hd)
+    v = qkv[:, (hq + hkv) * hd:].reshape(n, hkv, hd)
+    if qn is not None:
+        q, k = plain.rmsnorm(q, qn, eps), plain.rmsnorm(k, kn, eps)
+
+    def rot(x):
+        if cos is None:
+            return x
+        c, s = cos[pos0:pos0 + n], sin[pos0:pos0 + n]
+        part = x[..., :rotary_dim]
+        if interleaved:  # pairs (2i, 2i+1): bring them to the half layout, rotate, and back
+            half = np.concatenate([part[..., 0::2], part[..., 1::2]], axis=-1)
+            r = plain.rope(half, c, s)
+            back = np.empty_like(part)
+            back[..., 0::2], back[..., 1::2] = r[..., :rotary_dim // 2], r[..., rotary_dim // 2:]
+            part = back
+        else:
+            part = plain.rope(part, c, s)
+        return np.concatenate([part, x[..., rotary_dim:]], axis=-1)
+
+    return rot(q), rot(k), v
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hq, hkv, hd, rotary_dim, interleaved, norm, window", [
+    (6, 2, 48, 48, False, True, None),
+    (3, 3, 16, 16, True, False, None),
+    (8, 1, 80, 32, False, True, None),     # one kv head for all, partial rotation
+    (4, 2, 128, 128, False, True, 70),     # a window across page boundaries
+    (2, 1, 256, 64, True, True, 5),
+])
+def test_qkv_prep_and_attention(ops, dtype, hq, hkv, hd, rotary_dim, interleaved, norm, window):
+    """Two sequences, one prefilled in two chunks and then decoded, the other whole: every cut reads
+    the paged cache (and, windowed, its ring) and must equal attention over the whole sequence."""
+    rng = np.random.default_rng(hq * 1000 + hd)
+    eps, scale = 2e-5, 0.37 / np.sqrt(hd)
+    qn = (1 + 0.3 * rng.standard_normal(hd)).astype(np.float32) * 3 if norm else None
+    kn = (1 + 0.3 * rng.standard_normal(hd)).astype(np.float32) * 3 if norm else None
+    cos, sin = plain.rope_table(400, rotary_dim, 1234.5)
+    width = (hq + 2 * hkv) * hd
+    lens = {"a": 150, "b": 93}
+    data = {k: rng.standard_normal((n, width)).astype(np.float32) * (1.0 if norm else 2.0) for k, n in lens.items()}
+    if dtype == torch.bfloat16:
+        data = {k: bf(v) for k, v in data.items()}
+    want = {}
+    # plain.attention uses 1/sqrt(hd); fold our own scale in by scaling q beforehand
+    for key, qkv in data.items():
+        q, k, v = plain_prep(qkv, hq, hkv, hd, qn, kn, eps, cos, sin, rotary_dim, interleaved, 0)
+        if dtype == torch.bfloat16:
+            q, k = bf(q), bf(k)
+        want[key] = (q, plain.attention((q * np.float32(scale * np.sqrt(hd))).astype(np.float32), k, v,
+                                        window).reshape(lens[key], hq * hd))
+    h = Harness(hq, hkv, hd, dtype, window)
+    sa, sb = h.cache.open_slot(), h.cache.open_slot()
+    args = (dev(qn) if norm else None, dev(kn) if norm else None, eps, dev(cos), dev(sin), rotary_dim, interleaved,
+            scale)
+    tol = dict(rtol=2e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=2 ** -6, atol=2 ** -7)
+    got_a, got_b = [], []
+    # step 1: the first 70 tokens of a and all of b (windowed layers read this step's own rows)
+    q, o = h.step(ops, [(sa, 70), (sb, 93)], np.concatenate([data["a"][:70], data["b"]]), *args,
+                  from_step=window is not None)
+    np.testing.assert_allclose(q[:70, :hq * hd].reshape(70, hq, hd), want["a"][0][:70], **tol)
+    got_a.append(o[:70]), got_b.append(o[70:])
+    if window is None:
+        # step 2: 50 more tokens of a, at positions 70..119, reading the cache for the first 70
+        _, o = h.step(ops, [(sa, 50)], data["a"][70:120], *args)
+        got_a.append(o)
+        first = 120
+    else:
+        first = 70
+    # then a token by token, in a batch with nothing else
+    for i in range(first, 150):
+        _, o = h.step(ops, [(sa, 1)], data["a"][i:i + 1], *args)
+        got_a.append(o)
+    np.testing.assert_allclose(np.concatenate(got_a), want["a"][1], **tol)
+    np.testing.assert_allclose(np.concatenate(got_b), want["b"][1], **tol)
+
+
+def test_attention_finds_one_far_key(ops):
+    """Among 600 keys with scores near zero, one key 500 places back scores high: the output must be its value."""
+    hq, hkv, hd, n = 2, 1, 64, 600
+    rng = np.random.default_rng(9)
+    qkv = 0.01 * rng.standard_normal((n, (hq + 2) * hd)).astype(np.float32)
+    needle = 99
+    qkv[needle, hq * hd:(hq + 1) * hd] = 3.0  # its key
+    qkv[needle, (hq + 1) * hd:] = np.arange(hd)  # its value
+    qkv[n - 1, :hq * hd] = 3.0  # the last token's queries point at it
+    h = Harness(hq, hkv, hd, torch.float32)
+    slot = h.cache.open_slot()
+    h.step(ops, [(slot, n - 1)], qkv[:n - 1], None, None, 0.0, None, None, 0, False, 1.0)
+    _, o = h.step(ops, [(slot, 1)], qkv[n - 1:], None, None, 0.0, None, None, 0, False, 1.0)
+    np.testing.assert_allclose(o.reshape(hq, hd), np.tile(np.arange(hd, dtype=np.float32), (hq, 1)), atol=1e-3)
+
+
+def test_refusals_are_errors_not_results(ops):
+    from abacus_b200.engine.batch import Sequence, StepBatch
+    batch = StepBatch(1, 1, 0, "cuda").fill([Sequence(0, [0], 0, [])])
+    qkv = torch.zeros(1, 3 * 260, device="cuda")
+    with pytest.raises(ops.KernelRefused, match="head_dim"):
+        ops.qkv_prep(qkv, 1, 1, 260, batch, None, None, 0.0, None, None, 0, False, None)
+    with pytest.raises(ops.KernelError, match="not on the GPU"):
+        ops.swiglu(torch.zeros(2, 4), torch.zeros(2, 2))
