@@ -93,12 +93,17 @@ class TraceRun:
 
 # ------------------------------------------------------------------ comparison rules
 # float32: the engine and the plain implementation do the same float32 arithmetic in different
-# orders; logits are of order one, so differences beyond a few 1e-6 mean a fault.
-F32_ATOL, F32_RTOL = 5e-5, 5e-5
+# orders. Their distance is bounded by a small absolute/relative term plus the rounding noise that
+# float32 itself shows on that input: `noise` = max |plain float32 - plain float64|. The sharpened
+# weights above amplify rounding (measured: up to 1.4e-4 on four-layer configuration C), and a
+# limit below the reference's own noise would test nothing but luck.
+F32_ATOL, F32_RTOL, F32_NOISE = 5e-5, 5e-5, 3.0
 # bfloat16: against the plain implementation with its stored tensors rounded to bfloat16 at the
-# same places. What is left is single-ulp rounding flips (2^-8 relative) and their propagation:
-# at most 2 % of the largest logit, and a tiny KL divergence.
-BF16_REL_MAX, BF16_KL = 0.02, 2e-3
+# same places. What is left is single-ulp rounding flips and their propagation, a fraction of
+# the rounding noise of bfloat16 itself: `noise` = max |plain with bfloat16 storage - plain float32|
+# (measured: 0.2 to 1.3 on logits of scale 6 to 7). The limit is 2 % of the largest logit or a
+# quarter of that noise, whichever is larger, and a small KL divergence.
+BF16_REL_MAX, BF16_NOISE, BF16_KL = 0.02, 0.25, 2e-3
 
 
 def log_softmax64(x):
@@ -107,21 +112,21 @@ def log_softmax64(x):
     return x - np.log(np.exp(x).sum(axis=-1, keepdims=True))
 
 
-def assert_logits(got, want, dtype, what=""):
+def assert_logits(got, want, dtype, what="", noise=0.0):
     got, want = np.asarray(got, dtype=np.float32), np.asarray(want, dtype=np.float32)
     assert got.shape == want.shape, f"{what}: shape {got.shape} vs {want.shape}"
     assert np.isfinite(got).all(), f"{what}: logits are not finite"
     diff = np.abs(got - want)
     if dtype == "float32":
-        bad = diff > F32_ATOL + F32_RTOL * np.abs(want)
+        bad = diff > F32_ATOL + F32_RTOL * np.abs(want) + F32_NOISE * noise
         assert not bad.any(), (f"{what}: float32 logits differ by up to {diff.max():.3g} "
-                               f"(first bad row {np.argwhere(bad)[0][0]} of {got.shape[0]})")
+                               f"(first bad row {np.argwhere(bad)[0][0]} of {got.shape[0]}, noise {noise:.3g})")
     else:
         scale = np.abs(want).max()
+        limit = max(BF16_REL_MAX * scale, BF16_NOISE * noise)
         rows = diff.max(axis=-1)
-        assert rows.max() <= BF16_REL_MAX * scale, (
-            f"{what}: bfloat16 logits differ by {rows.max():.3g} at row {rows.argmax()} "
-            f"(limit {BF16_REL_MAX * scale:.3g}, scale {scale:.3g})")
+        assert rows.max() <= limit, (f"{what}: bfloat16 logits differ by {rows.max():.3g} at row {rows.argmax()} "
+                                     f"(limit {limit:.3g}, scale {scale:.3g}, noise {noise:.3g})")
         lp, lq = log_softmax64(want), log_softmax64(got)
         kl = (np.exp(lp) * (lp - lq)).sum(-1)
         assert kl.max() <= BF16_KL, f"{what}: KL {kl.max():.3g} at row {kl.argmax()} (limit {BF16_KL})"

@@ -203,6 +203,17 @@ def forward(cfg, w, tokens, rnd=None, schedule=None):
     return linear(xn, head)  # src/model.c:102-103, 322-325
 
 
+def forward64(cfg, w, tokens, schedule=None):
+    """The same formulas evaluated in float64: what float32 results scatter around. The distance
+    between forward() and this is the rounding noise of float32 for that input."""
+    global F32
+    keep, F32 = F32, np.float64
+    try:
+        return forward(cfg, {k: v.astype(np.float64) for k, v in w.items()}, tokens, schedule=schedule)
+    finally:
+        F32 = keep
+
+
 def load(folder):
     cfg = read_config(f"{folder}/config.json")
     return cfg, read_safetensors(f"{folder}/model.safetensors")

@@ -39,12 +39,26 @@ class Case:
         for i in (1, 2, 3):
             self.requests[f"first{i}"] = random_tokens(rng, i, self.vocab)
         self.rnd = plain.bf16_round if dtype == "bfloat16" else None
-        self._want = {}
+        self.dtype = dtype
+        self._want, self._noise = {}, {}
 
     def want(self, rid):
         if rid not in self._want:
             self._want[rid] = plain.forward(self.cfg, self.w, self.requests[rid], rnd=self.rnd)
         return self._want[rid]
+
+    def noise(self, rid):
+        """The rounding noise of this dtype on this request (see helpers.assert_logits)."""
+        if rid not in self._noise:
+            exact = plain.forward(self.cfg, self.w, self.requests[rid])
+            if self.dtype == "bfloat16":
+                self._noise[rid] = float(np.abs(self.want(rid) - exact).max())
+            else:
+                self._noise[rid] = float(np.abs(exact - plain.forward64(self.cfg, self.w, self.requests[rid])).max())
+        return self._noise[rid]
+
+    def check(self, got, rid, rows, what):
+        assert_logits(got, self.want(rid)[rows], self.dtype, f"{what} of {rid}", noise=self.noise(rid))
 
 
 @pytest.fixture(scope="module")
@@ -66,7 +80,7 @@ def test_replay(folders, tmp_path, name, dtype):
         for rid in [f"r{i}" for i in range(len(LENGTHS))]:
             n = len(R[rid])
             got = run.step([(rid, R[rid], list(range(n)))], end=[rid])
-            assert_logits(got.reshape(n, V), case.want(rid), dtype, f"{name} {rid} whole")
+            case.check(got.reshape(n, V), rid, slice(0, n), f"{name} whole")
         # 2. last 32 one by one
         for rid in [f"r{i}" for i in range(len(LENGTHS))]:
             toks, n = R[rid], len(R[rid])
@@ -77,7 +91,7 @@ def test_replay(folders, tmp_path, name, dtype):
             for i in range(head, n):
                 rows.append(run.step([(rid, [toks[i]], [0])], end=[rid] if i == n - 1 else []).reshape(1, V))
             first = head - 1 if head else 0
-            assert_logits(np.concatenate(rows), case.want(rid)[first:], dtype, f"{name} {rid} last 32 one by one")
+            case.check(np.concatenate(rows), rid, slice(first, n), f"{name} last 32 one by one")
         # 3. unequal batches, shorter requests end earlier, batch after batch
         for b in batches:
             split = {rid: max(1, len(R[rid]) - (7 + 5 * i)) for i, rid in enumerate(b)}  # prompt | decoded part
@@ -85,8 +99,8 @@ def test_replay(folders, tmp_path, name, dtype):
                            end=[rid for rid in b if split[rid] == len(R[rid])])
             at = 0
             for rid in b:
-                assert_logits(got[at * V:(at + split[rid]) * V].reshape(split[rid], V), case.want(rid)[:split[rid]],
-                              dtype, f"{name} batch {b} prompt of {rid}")
+                case.check(got[at * V:(at + split[rid]) * V].reshape(split[rid], V), rid, slice(0, split[rid]),
+                           f"{name} batch {b} prompt")
                 at += split[rid]
             live = [rid for rid in b if split[rid] < len(R[rid])]
             k = 0
@@ -94,9 +108,8 @@ def test_replay(folders, tmp_path, name, dtype):
                 ends = [rid for rid in live if split[rid] + k == len(R[rid]) - 1]
                 got = run.step([(rid, [R[rid][split[rid] + k]], [0]) for rid in live], end=ends)
                 for j, rid in enumerate(live):
-                    assert_logits(got[j * V:(j + 1) * V].reshape(1, V),
-                                  case.want(rid)[split[rid] + k:split[rid] + k + 1], dtype,
-                                  f"{name} batch {b} decode {k} of {rid}")
+                    case.check(got[j * V:(j + 1) * V].reshape(1, V), rid, slice(split[rid] + k, split[rid] + k + 1),
+                               f"{name} batch {b} decode {k}")
                 live = [rid for rid in live if rid not in ends]
                 k += 1
         # 4. long decode, one token at a time after a 40-token prompt
@@ -104,17 +117,17 @@ def test_replay(folders, tmp_path, name, dtype):
         rows = [run.step([("long", toks[:40], [39])]).reshape(1, V)]
         for i in range(40, n):
             rows.append(run.step([("long", [toks[i]], [0])], end=["long"] if i == n - 1 else []).reshape(1, V))
-        assert_logits(np.concatenate(rows), case.want("long")[39:], dtype, f"{name} long decode")
+        case.check(np.concatenate(rows), "long", slice(39, n), f"{name} long decode")
         # 5. the first tokens of a sequence, as one batch of very short prompts and then decoded
         ids = ["first1", "first2", "first3"]
         got = run.step([(rid, R[rid][:1], [0]) for rid in ids], end=["first1"])
         for j, rid in enumerate(ids):
-            assert_logits(got[j * V:(j + 1) * V].reshape(1, V), case.want(rid)[:1], dtype, f"{name} {rid} first token")
+            case.check(got[j * V:(j + 1) * V].reshape(1, V), rid, slice(0, 1), f"{name} first token")
         got = run.step([(rid, R[rid][1:2], [0]) for rid in ids[1:]], end=["first2"])
         for j, rid in enumerate(ids[1:]):
-            assert_logits(got[j * V:(j + 1) * V].reshape(1, V), case.want(rid)[1:2], dtype, f"{name} {rid} second token")
+            case.check(got[j * V:(j + 1) * V].reshape(1, V), rid, slice(1, 2), f"{name} second token")
         got = run.step([("first3", R["first3"][2:3], [0])], end=["first3"])
-        assert_logits(got.reshape(1, V), case.want("first3")[2:3], dtype, f"{name} first3 third token")
+        case.check(got.reshape(1, V), "first3", slice(2, 3), f"{name} third token")
         # a step that wants nothing writes nothing
         assert run.step([("quiet", R["r2"], [])], end=["quiet"]) is None
     finally:
