@@ -1,0 +1,347 @@
+// out[M, N] = x[M, K] . w[N, K]^T in bfloat16 on the 5th-generation tensor cores (tcgen05),
+// float32 accumulation in tensor memory, operands brought in by TMA.
+//
+// One CTA computes a tile D[128, BN] = P_tile . Q_tile^T over a range of K:
+//   warp 0      one thread issues TMA loads of [128 x 64] of P and [BN x 64] of Q into a ring of
+//               shared-memory stages (128-byte swizzle), signalling a "full" mbarrier per stage;
+//   warp 1      allocates BN tensor-memory columns; one thread issues four tcgen05.mma
+//               (128 x BN x 16) per stage and commits to the stage's "empty" mbarrier, and at the
+//               end to the "accumulator ready" mbarrier;
+//   warps 2-5   read the accumulator with tcgen05.ld (each warp its own 32 lanes) and store it.
+// P and Q are the two matrices in either order: with many rows of x (prefill) P = x, so lanes are
+// tokens; with few rows (decode) P = w, so the 128 lanes are output features, the tokens are the
+// BN columns (16..64) and no tensor-core work is spent on padding. The weights stream through
+// once either way.
+//
+// Split K: grid.z CTAs share a tile, each over its own K range. Each writes its float32 partial
+// tile to scratch memory and takes a ticket; the last one adds the partials in split order
+// (so the result does not depend on which CTA came last) and stores the tile.
+//
+// K may be any multiple of 8 (a TMA row pitch must be a multiple of 16 bytes); rows beyond M or
+// N and columns beyond K are zero-filled by TMA. Other shapes are refused, not approximated.
+// Formula: src/model.c:299, 302, 307, 309, 324.
+#define ABK_DEFINE_ERROR
+#include "common.cuh"
+#include "tc_common.cuh"
+#include <mutex>
+#include <unordered_map>
+
+#define TILE_P 128
+#define TILE_K 64
+#define GEMM_THREADS 192
+
+struct GemmTc {
+    void *out;
+    long long stride_p, stride_q;  // out element (p, q) is out[p * stride_p + q * stride_q]
+    int P, Q, K;
+    int k_blocks, k_blocks_per_split, splits;
+    float *partials;  // [splits, tiles, BN, 128] when splits > 1
+    int *tickets;     // [tiles], zero before and after the launch
+    int *status;
+    int vec;  // stride_q == 1 and every 16-column run of a row starts on a 16-byte boundary
+};
+
+template <int BN, int STAGES> struct GemmSmem {
+    static constexpr int A_BYTES = TILE_P * TILE_K * 2, B_BYTES = BN * TILE_K * 2;
+    static constexpr int BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /* alignment */ + 256 /* barriers */;
+};
+
+// 16 consecutive results of one row, stored as 16-byte vectors.
+__device__ __forceinline__ void store16(float *dst, const uint32_t *v) {
+#pragma unroll
+    for (int j = 0; j < 16; j += 4) *(uint4 *)(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+}
+__device__ __forceinline__ void store16(__nv_bfloat16 *dst, const uint32_t *v) {
+    uint32_t h[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+        h[j] = *(uint32_t *)&t;
+    }
+    *(uint4 *)dst = make_uint4(h[0], h[1], h[2], h[3]);
+    *(uint4 *)(dst + 8) = make_uint4(h[4], h[5], h[6], h[7]);
+}
+
+template <int BN, int STAGES, typename TO>
+__global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p,
+                                                               const __grid_constant__ CUtensorMap map_q, GemmTc g) {
+    using S = GemmSmem<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *a_tiles = smem, *b_tiles = smem + STAGES * S::A_BYTES;
+    uint64_t *full = (uint64_t *)(smem + STAGES * (S::A_BYTES + S::B_BYTES));
+    uint64_t *empty = full + STAGES, *acc_ready = empty + STAGES;
+    uint32_t *tmem_holder = (uint32_t *)(acc_ready + 1);
+    volatile int *flags = (volatile int *)(tmem_holder + 1);  // [0]: a wait ran out; [1]: ticket
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p0 = blockIdx.x * TILE_P, q0 = blockIdx.y * BN, split = blockIdx.z;
+    const int kb_begin = split * g.k_blocks_per_split;
+    const int kb_end = min(g.k_blocks, kb_begin + g.k_blocks_per_split);
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) tc::mbar_init(&full[s], 1), tc::mbar_init(&empty[s], 1);
+        tc::mbar_init(acc_ready, 1);
+        flags[0] = 0, flags[1] = 0;
+        tc::mbar_init_fence();
+        tc::tma_prefetch_map(&map_p), tc::tma_prefetch_map(&map_q);
+    }
+    if (warp == 1) tc::tmem_alloc(tmem_holder, TMEM_COLS);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem = *tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = kb_begin; kb < kb_end; kb++, issued++) {
+                int s = issued % STAGES;
+                if (!tc::mbar_wait(&empty[s], ((issued / STAGES) & 1) ^ 1)) {
+                    flags[0] = 1;
+                    break;
+                }
+                tc::mbar_expect_tx(&full[s], S::A_BYTES + S::B_BYTES);
+                tc::tma_load_2d(a_tiles + s * S::A_BYTES, &map_p, kb * TILE_K, p0, &full[s]);
+                tc::tma_load_2d(b_tiles + s * S::B_BYTES, &map_q, kb * TILE_K, q0, &full[s]);
+            }
+            if (flags[0]) {  // let the copies still in flight land before the CTA's memory goes away
+                for (int i = max(0, issued - STAGES); i < issued; i++) tc::mbar_wait(&full[i % STAGES], (i / STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::idesc_bf16_f32(TILE_P, BN);
+            int done = 0;
+            for (int kb = kb_begin; kb < kb_end; kb++, done++) {
+                int s = done % STAGES;
+                if (!tc::mbar_wait(&full[s], (done / STAGES) & 1)) {
+                    flags[0] = 1;
+                    break;
+                }
+                tc::fence_after_sync();
+                uint32_t a = tc::smem_addr(a_tiles + s * S::A_BYTES), b = tc::smem_addr(b_tiles + s * S::B_BYTES);
+#pragma unroll
+                for (int k = 0; k < TILE_K / 16; k++)
+                    tc::mma_ss(tmem, tc::smem_desc_k_sw128(a + k * 32), tc::smem_desc_k_sw128(b + k * 32), idesc,
+                               done > 0 || k > 0);
+                tc::mma_commit(&empty[s]);
+            }
+            tc::mma_commit(acc_ready);
+        }
+    } else {
+        // epilogue: warp w reads lanes 32 * (w % 4) .. + 31 of the accumulator
+        const int quarter = warp & 3, row = quarter * 32 + lane, p = p0 + row;
+        bool ok = tc::mbar_wait(acc_ready, 0);
+        if (!ok) flags[0] = 1;
+        tc::fence_after_sync();
+        const int tiles = gridDim.x * gridDim.y, tile = blockIdx.y * gridDim.x + blockIdx.x;
+        const bool direct = g.splits == 1;
+        float *mine = direct ? nullptr : g.partials + ((long long)split * tiles + tile) * (BN * TILE_P);
+        TO *out = (TO *)g.out;
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t v[16];
+                tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + c0, v);
+                tc::tmem_ld_wait();
+                if (direct && g.vec && p < g.P && q0 + c0 + 16 <= g.Q) {
+                    store16(out + (long long)p * g.stride_p + q0 + c0, v);
+                } else if (direct) {
+                    if (p < g.P) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (q0 + c0 + j < g.Q)
+                                out[(long long)p * g.stride_p + (long long)(q0 + c0 + j) * g.stride_q] =
+                                    from_float<TO>(__uint_as_float(v[j]));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) mine[(c0 + j) * TILE_P + row] = __uint_as_float(v[j]);
+                }
+            }
+        }
+        if (!direct) {
+            // the last CTA of this tile to get here adds up all partials, in split order
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) flags[1] = atomicAdd(&g.tickets[tile], 1);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (flags[1] == g.splits - 1) {
+                __threadfence();
+                if (p < g.P) {
+                    for (int c = 0; c < BN && q0 + c < g.Q; c++) {
+                        float sum = 0.0f;
+                        for (int s = 0; s < g.splits; s++)
+                            sum += __ldcg(g.partials + ((long long)s * tiles + tile) * (BN * TILE_P) + c * TILE_P + row);
+                        out[(long long)p * g.stride_p + (long long)(q0 + c) * g.stride_q] = from_float<TO>(sum);
+                    }
+                }
+                if (threadIdx.x == 64) g.tickets[tile] = 0;
+            }
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (flags[0] && threadIdx.x == 0) atomicOr(g.status + 1, 1);
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_free(tmem, TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void *ptr;
+    long long rows, cols, ld;
+    int box_rows;
+    bool operator==(const MapKey &o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey &k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows, h = h * 1000003u ^ (size_t)k.cols;
+        return h * 1000003u ^ (size_t)k.ld ^ ((size_t)k.box_rows << 48);
+    }
+};
+
+// A tensor map over a row-major bfloat16 matrix [rows, cols] with row pitch ld: boxes of
+// [box_rows, 64] elements, 128-byte swizzle, zeros outside. Maps are kept by address and shape.
+static int tensor_map(const void *ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap *out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex lock;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> guard(lock);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return 0;
+    }
+    EncodeTiled enc = encode_tiled();
+    if (!enc) ABK_REFUSE("gemm_tc: the driver gives no cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TILE_K, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void *)ptr, dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) ABK_REFUSE("gemm_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = *out;
+    return 0;
+}
+
+template <int BN, int STAGES, typename TO>
+static int launch(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g, dim3 grid, cudaStream_t s) {
+    auto kernel = gemm_tc_kernel<BN, STAGES, TO>;
+    static bool configured = false;
+    constexpr int bytes = GemmSmem<BN, STAGES>::BYTES;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    kernel<<<grid, GEMM_THREADS, bytes, s>>>(mp, mq, g);
+    return ABK_LAUNCH_RESULT();
+}
+
+template <typename TO>
+static int launch_bn(int bn, const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g, dim3 grid, cudaStream_t s) {
+    switch (bn) {
+    case 16: return launch<16, 8, TO>(mp, mq, g, grid, s);
+    case 32: return launch<32, 8, TO>(mp, mq, g, grid, s);
+    case 64: return launch<64, 6, TO>(mp, mq, g, grid, s);
+    case 128: return launch<128, 3, TO>(mp, mq, g, grid, s);
+    case 256: return launch<256, 2, TO>(mp, mq, g, grid, s);
+    }
+    return ABK_REFUSED;
+}
+
+// Scratch the caller must provide for split K: how many floats and tickets this product may use.
+extern "C" long long abk_gemm_tc_scratch_floats() { return 8ll << 20; }
+extern "C" int abk_gemm_tc_scratch_tickets() { return 1 << 16; }
+
+// x [M, K] and w [N, K] bfloat16 with row pitches ldx, ldw (elements); out [M, N] bfloat16 or
+// float32 with row pitch ldo. scratch: float32 [abk_gemm_tc_scratch_floats()]; tickets: int32
+// [abk_gemm_tc_scratch_tickets()], all zero; status: int32 [>= 2], word 1 is set if a wait ran out.
+// force_bn / force_swap / force_splits (0 / -1 / 0: choose) pin the configuration, for tests.
+extern "C" int abk_gemm_tc(const void *x, const void *w, void *out, int out_dtype, int M, int N, int K, long long ldx,
+                           long long ldw, long long ldo, float *scratch, int *tickets, int *status, int force_bn,
+                           int force_swap, int force_splits, void *stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8)
+        ABK_REFUSE("gemm_tc: K = %d and the row pitches %lld, %lld must be multiples of 8", K, ldx, ldw);
+    if (((uintptr_t)x | (uintptr_t)w) & 15) ABK_REFUSE("gemm_tc: operands must be 16-byte aligned");
+    bool swap = force_swap >= 0 ? force_swap != 0 : M <= 64;
+    int bn;
+    if (swap) {  // columns are tokens
+        bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    } else {  // columns are output features
+        long long tiles256 = (long long)((M + TILE_P - 1) / TILE_P) * ((N + 255) / 256);
+        bn = N > 128 && tiles256 >= 148 ? 256 : N > 64 ? 128 : 64;
+    }
+    if (force_bn) bn = force_bn;
+    int P = swap ? N : M, Q = swap ? M : N;
+    if (swap && M > bn && M > 256) ABK_REFUSE("gemm_tc: %d rows do not fit the swapped layout", M);
+    dim3 grid((P + TILE_P - 1) / TILE_P, (Q + bn - 1) / bn, 1);
+    if (grid.y > 65535) ABK_REFUSE("gemm_tc: too many column tiles (%u)", grid.y);
+    int k_blocks = (K + TILE_K - 1) / TILE_K;
+    long long tiles = (long long)grid.x * grid.y;
+    int splits = 1;
+    if (tiles < 112) {  // too few tiles to fill 148 SMs: share tiles along K, at least 2 k-blocks each
+        splits = (int)((148 + tiles - 1) / tiles);
+        if (splits > k_blocks / 2) splits = k_blocks / 2;
+        if (splits < 1) splits = 1;
+    }
+    if (force_splits) splits = force_splits;
+    if (splits > k_blocks) splits = k_blocks;
+    int per = (k_blocks + splits - 1) / splits;
+    splits = (k_blocks + per - 1) / per;
+    if (splits > 1) {
+        if (tiles > abk_gemm_tc_scratch_tickets() ||
+            (long long)splits * tiles * bn * TILE_P > abk_gemm_tc_scratch_floats())
+            splits = 1, per = k_blocks;
+    }
+    grid.z = splits;
+
+    CUtensorMap mx, mw;
+    int rc = tensor_map(x, M, K, ldx, swap ? bn : TILE_P, &mx);
+    if (rc) return rc;
+    rc = tensor_map(w, N, K, ldw, swap ? TILE_P : bn, &mw);
+    if (rc) return rc;
+    GemmTc g;
+    g.out = out, g.P = P, g.Q = Q, g.K = K;
+    g.stride_p = swap ? 1 : ldo, g.stride_q = swap ? ldo : 1;
+    g.k_blocks = k_blocks, g.k_blocks_per_split = per, g.splits = splits;
+    g.partials = scratch, g.tickets = tickets, g.status = status;
+    int esize = out_dtype == ABK_BF16 ? 2 : 4;
+    g.vec = !swap && ((uintptr_t)out % 16 == 0) && (ldo * esize) % 16 == 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const CUtensorMap &mp = swap ? mw : mx, &mq = swap ? mx : mw;
+    if (out_dtype == ABK_BF16) rc = launch_bn<__nv_bfloat16>(bn, mp, mq, g, grid, s);
+    else rc = launch_bn<float>(bn, mp, mq, g, grid, s);
+    if (rc == ABK_REFUSED) ABK_REFUSE("gemm_tc: no kernel for a column tile of %d", bn);
+    return rc;
+}

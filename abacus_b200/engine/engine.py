@@ -103,7 +103,11 @@ class Engine:
 
     def check_status(self):
         """Raise if a kernel reported a fault (a bounded wait that ran out, a token out of range)."""
-        status = self.model.status.tolist()
+        from ..kernels import ops
+        shared = ops.kernel_status(self.model.ctx.device)
+        status = self.model.status.tolist() + shared.tolist()
         if any(status):
             self.model.status.zero_()
-            raise RuntimeError(f"a kernel reported a fault: status words {status}")
+            shared.zero_()
+            raise RuntimeError(f"a kernel reported a fault (a token outside the vocabulary, or a wait that "
+                               f"ran out): status words {status}")

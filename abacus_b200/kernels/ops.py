@@ -191,10 +191,53 @@ def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cac
     attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=from_step)
 
 
+class _Scratch:
+    """Per-device scratch of the kernels that need some: split-K partial tiles and their tickets,
+    attention partials, and the status words a kernel sets when one of its bounded waits runs out."""
+    _of_device = {}
+
+    def __init__(self, device):
+        lib = load_module("gemm_tc")
+        lib.abk_gemm_tc_scratch_floats.restype = ctypes.c_longlong
+        self.gemm_floats = torch.empty(lib.abk_gemm_tc_scratch_floats(), dtype=torch.float32, device=device)
+        self.gemm_tickets = torch.zeros(lib.abk_gemm_tc_scratch_tickets(), dtype=torch.int32, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+
+    @classmethod
+    def of(cls, device):
+        key = (device.type, device.index)
+        if key not in cls._of_device:
+            cls._of_device[key] = cls(device)
+        return cls._of_device[key]
+
+
+def kernel_status(device):
+    """Status words of the device's kernels: all zero unless a kernel gave up on a wait."""
+    return _Scratch.of(device).status
+
+
 def gemm_tc_takes(x, w, out):
-    """Whether the tensor-core kernel takes this product (else the CUDA-core kernel runs it)."""
-    return False
+    """Whether the tensor-core kernel takes this product (else the CUDA-core kernel runs it):
+    bfloat16 operands, K and both row pitches multiples of 8, 16-byte aligned."""
+    k = w.shape[1]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 and x.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1)
 
 
-def gemm_tc(x, w, out, m=None):
-    raise KernelRefused("the tensor-core matrix product is not built for this shape")
+def gemm_tc(x, w, out, m=None, tile_n=0, swap=-1, splits=0):
+    """out[:m] = x[:m] . w^T in bfloat16 on the tcgen05 tensor cores, float32 accumulation.
+
+    tile_n, swap and splits pin the tile configuration (tests); 0 / -1 / 0 let the kernel choose.
+    """
+    _need_cuda(x, w, out)
+    lib = load_module("gemm_tc")
+    sc = _Scratch.of(x.device)
+    m = x.shape[0] if m is None else m
+    n, k = w.shape
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert x.shape[1] == k and out.shape[1] == n and x.shape[0] >= m and out.shape[0] >= m
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(lib, lib.abk_gemm_tc(_p(x), _p(w), _p(out), _i(_dt(out)), _i(m), _i(n), _i(k), _ll(x.stride(0)),
+                                _ll(w.stride(0)), _ll(out.stride(0)), _p(sc.gemm_floats), _p(sc.gemm_tickets),
+                                _p(sc.status), _i(tile_n), _i(swap), _i(splits), _stream()), "gemm_tc")

@@ -276,3 +276,60 @@ def test_refusals_are_errors_not_results(ops):
         ops.qkv_prep(qkv, 1, 1, 260, batch, None, None, 0.0, None, None, 0, False, None)
     with pytest.raises(ops.KernelError, match="not on the GPU"):
         ops.swiglu(torch.zeros(2, 4), torch.zeros(2, 2))
+
+
+# ------------------------------------------------------------------ tensor-core matrix product
+
+def _gemm_case(ops, m, n, k, out_dtype, rng, **pin):
+    x, w = bf(rng.standard_normal((m, k))), bf(rng.standard_normal((n, k)))
+    out = torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda")
+    ops.gemm_tc(dev(x, torch.bfloat16), dev(w, torch.bfloat16), out, **pin)
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all(), (m, n, k, pin)
+    tol = 1e-5 * np.sqrt(k) * 4 if out_dtype == torch.float32 else 2 ** -8 * np.abs(want).max()
+    np.testing.assert_allclose(got, want, rtol=0 if out_dtype == torch.float32 else 2 ** -8, atol=tol,
+                               err_msg=str((m, n, k, pin)))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tc_every_tile_configuration(ops, out_dtype):
+    """Each column tile, both operand orders, with and without split K, on sizes that leave ragged
+    edges in every direction (M, N no tile multiples; K not a multiple of 64)."""
+    rng = np.random.default_rng(21)
+    for tile_n in (16, 32, 64, 128, 256):
+        for swap in (0, 1):
+            for splits in (1, 3):
+                m = min(tile_n, 37) if swap else 150
+                _gemm_case(ops, m, 389 if swap else 264, 328, out_dtype, rng, tile_n=tile_n, swap=swap, splits=splits)
+    assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 128, 64), (1, 1024, 2048), (8, 4096, 1024), (64, 1000, 72), (65, 192, 96),
+                                      (300, 389, 96), (2048, 1024, 1024), (5, 151936, 128), (130, 70, 8)])
+def test_gemm_tc_chosen_configuration(ops, m, n, k):
+    rng = np.random.default_rng(m + n + k)
+    _gemm_case(ops, m, n, k, torch.float32, rng)
+    _gemm_case(ops, m, n, k, torch.bfloat16, rng)
+    assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
+
+
+def test_gemm_tc_split_k_is_deterministic_and_leaves_its_tickets_at_zero(ops):
+    rng = np.random.default_rng(22)
+    x, w = dev(bf(rng.standard_normal((8, 3072))), torch.bfloat16), dev(bf(rng.standard_normal((1024, 3072))), torch.bfloat16)
+    outs = []
+    for _ in range(4):
+        out = torch.empty(8, 1024, device="cuda")
+        ops.gemm_tc(x, w, out)
+        outs.append(out)
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+    from abacus_b200.kernels.ops import _Scratch
+    assert int(_Scratch.of(torch.device("cuda", 0)).gemm_tickets.abs().sum()) == 0
+
+
+def test_gemm_tc_refuses_what_tma_cannot_address(ops):
+    x, w = torch.zeros(4, 20, dtype=torch.bfloat16, device="cuda"), torch.zeros(16, 20, dtype=torch.bfloat16, device="cuda")
+    out = torch.empty(4, 16, device="cuda")
+    assert not ops.gemm_tc_takes(x, w, out)  # K = 20 is no multiple of 8: the linear layer uses the CUDA-core kernel
+    with pytest.raises(ops.KernelRefused, match="multiples of 8"):
+        ops.gemm_tc(x, w, out)
