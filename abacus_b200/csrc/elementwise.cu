@@ -204,3 +204,23 @@ extern "C" int abk_qkv_prep(void *qkv, int dtype, int n_tokens, int n_heads, int
         qkv_prep_kernel<float><<<grid, PREP_WARPS * 32, 0, s>>>(p);
     return ABK_LAUNCH_RESULT();
 }
+
+// ------------------------------------------------------------------ next decode step
+// Moves a decode step one position on without the host: every real row's position, and every
+// sequence's start and length, go up by one.
+__global__ void advance_decode_kernel(const int *token_seq, int *token_pos, int n_rows, int *seq_pos0,
+                                      int *seq_len_after, int n_seqs) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_rows && token_seq[i] >= 0) token_pos[i] += 1;
+    if (i < n_seqs) seq_pos0[i] += 1, seq_len_after[i] += 1;
+}
+
+extern "C" int abk_advance_decode(const int *token_seq, int *token_pos, int n_rows, int *seq_pos0, int *seq_len_after,
+                                  int n_seqs, void *stream) {
+    int n = n_rows > n_seqs ? n_rows : n_seqs;
+    if (n <= 0) return 0;
+    advance_decode_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(token_seq, token_pos, n_rows, seq_pos0,
+                                                                            seq_len_after, n_seqs);
+    return ABK_LAUNCH_RESULT();
+}
+

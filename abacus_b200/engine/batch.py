@@ -49,8 +49,10 @@ class StepBatch:
         self.any_continuation = False
         self._sent = None
 
-    def fill(self, sequences):
-        """Write the step described by `sequences` (list of Sequence) and send it to the device."""
+    def fill(self, sequences, pad_logits=False):
+        """Write the step described by `sequences` (list of Sequence) and send it to the device.
+        pad_logits: logits are made for as many rows as this StepBatch has room for (a captured graph
+        needs a fixed number); the rows beyond the wanted ones repeat row 0 and are ignored."""
         h = self._h
         if self._sent is not None:
             self._sent.synchronize()  # the last copy must have read the host buffer before it is rewritten
@@ -62,6 +64,7 @@ class StepBatch:
         h["tokens"][:] = 0
         h["token_pos"][:] = 0
         h["seq_slot"][:] = 0
+        h["logit_rows"][:] = 0
         h["seq_pos0"][:] = 0
         h["seq_len_after"][:] = 0
         row, lr = 0, 0
@@ -82,6 +85,8 @@ class StepBatch:
             row += n
         h["seq_start"][len(sequences):] = row
         self.n_tokens, self.n_seqs, self.n_logit_rows = n_tokens, len(sequences), n_logits
+        if pad_logits:
+            self.n_logit_rows = self.cap_logits
         self.sequences = list(sequences)  # host view, for mixers that walk the sequences themselves
         self.max_position = max((s.start + len(s.tokens) - 1 for s in sequences), default=0)
         self.max_len_after = self.max_position + 1
@@ -91,4 +96,16 @@ class StepBatch:
         if self.device.type == "cuda":
             self._sent = torch.cuda.Event()
             self._sent.record()
+        return self
+
+    def advance_on_device(self):
+        """Every sequence moves one position on (a decode step follows a decode step); the tokens are
+        left as they are on the device. The host's view follows."""
+        from ..kernels import ops
+        ops.advance_decode(self)
+        for s in self.sequences:
+            s.start += 1
+        self.max_position += 1
+        self.max_len_after += 1
+        self.any_continuation = True
         return self

@@ -15,6 +15,7 @@ from ..config.registry import load_config
 from ..models.model import Model
 from ..weights.loader import load_folder
 from .batch import Sequence, StepBatch
+from .graphs import DecodeGraphs
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
           "f32": torch.float32}
@@ -44,7 +45,7 @@ def load_model(folder, dtype="bfloat16", device=None):
 
 
 class Engine:
-    def __init__(self, model, max_tokens, max_slots=None, max_context=None):
+    def __init__(self, model, max_tokens, max_slots=None, max_context=None, use_graphs=True):
         self.model = model
         spec = model.spec
         context = min(max_context or spec.max_positions, spec.max_positions)
@@ -53,6 +54,7 @@ class Engine:
         self.max_context = self.cache.max_context
         model.prepare(self.max_context)
         self.vocab = spec.vocab
+        self.graphs = DecodeGraphs(self) if use_graphs else None
 
     # ------------------------------------------------------------ sequences
     def open(self):
@@ -93,10 +95,15 @@ class Engine:
         """Run one step; returns float32 logits [wanted rows, vocab] on the device, in the order of
         the entries and of each entry's `want`."""
         seqs = self.plan(entries)
-        n_rows = sum(len(s.tokens) for s in seqs)
-        batch = StepBatch(n_rows, len(seqs), sum(len(s.want) for s in seqs), self.model.ctx.device).fill(seqs)
-        logits = self.model.forward(batch, self.cache)
-        self.last_batch = batch
+        if self.graphs is not None and self.graphs.takes(seqs):  # a plain decode step: replay its graph
+            graph = self.graphs.get(seqs)
+            logits = graph.run(seqs)
+            self.last_batch = graph.batch
+        else:
+            n_rows = sum(len(s.tokens) for s in seqs)
+            batch = StepBatch(n_rows, len(seqs), sum(len(s.want) for s in seqs), self.model.ctx.device).fill(seqs)
+            logits = self.model.forward(batch, self.cache)
+            self.last_batch = batch
         for s in seqs:
             self.cache.advance(s.slot, len(s.tokens))
         return logits

@@ -120,6 +120,13 @@ def qkv_prep(qkv, n_heads, n_kv_heads, head_dim, batch, q_norm, k_norm, eps, cos
         _stream()), "qkv_prep")
 
 
+def advance_decode(batch):
+    """Every row of a decode step one position on, on the device (engine.batch.StepBatch.advance_on_device)."""
+    lib = load_module("elementwise")
+    _check(lib, lib.abk_advance_decode(_p(batch.token_seq), _p(batch.token_pos), _i(batch.n_rows), _p(batch.seq_pos0),
+                                       _p(batch.seq_len_after), _i(batch.n_seqs), _stream()), "advance_decode")
+
+
 def attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False):
     """Causal grouped-query attention of every token of the step (src/model.c:197-211).
 
@@ -188,7 +195,43 @@ def sample_topk(logits, temperature, top_k, rng_state, out, n_rows=None, rng_ind
 def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, ws=None):
     """Attention of a step: picks the kernel for the phase and sizes; every case the faster kernels
     do not take goes to the general one."""
-    attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=from_step)
+    if (batch.is_decode and not from_step and ws is not None and qkv.dtype == torch.bfloat16
+            and attention_decode_takes(n_heads, n_kv_heads, head_dim, cache)):
+        attention_decode(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws)
+    else:
+        attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=from_step)
+
+
+def attention_decode_takes(n_heads, n_kv_heads, head_dim, cache):
+    group = n_heads // n_kv_heads
+    smem = 4 * 64 * head_dim * 2 + 4 * group * (head_dim + 2) * 4 + 64
+    return head_dim in (64, 128, 256) and cache.tokens_per_page == 64 and smem <= 200 * 1024
+
+
+def attention_decode(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, max_positions=None):
+    """One new token per row against the paged bfloat16 cache, split along the keys (src/model.c:197-211).
+
+    max_positions bounds every row's position + 1 (it sizes the grid and the scratch); by default
+    the step's own maximum. A captured graph passes the bound it was captured for.
+    """
+    _need_cuda(qkv, out)
+    lib = load_module("attention_decode")
+    lib.abk_attention_decode_scratch_floats.restype = ctypes.c_longlong
+    n = batch.n_rows
+    row = (n_heads + 2 * n_kv_heads) * head_dim
+    assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
+    assert qkv.is_contiguous() and qkv.shape[1] == row and out.is_contiguous() and out.shape[1] == n_heads * head_dim
+    max_positions = max_positions or getattr(batch, "position_bound", None) or batch.max_len_after
+    if batch.max_len_after > max_positions:
+        raise KernelError(f"a row at position {batch.max_len_after - 1} is beyond the bound {max_positions}")
+    chunks = -(-max_positions // 128)
+    floats = lib.abk_attention_decode_scratch_floats(_i(n), _i(n_heads), _i(head_dim), _i(chunks))
+    scratch = ws.get("attention_partials", (floats,), torch.float32)
+    _check(lib, lib.abk_attention_decode(
+        _p(qkv), _ll(row), _p(out), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _i(window or 0),
+        _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(cache.k), _p(cache.v), _p(cache.page_table),
+        _i(cache.table_width), _i(cache.ring_pages), _i(cache.tokens_per_page), _i(max_positions), _p(scratch),
+        _p(kernel_status(qkv.device)), _stream()), "attention_decode")
 
 
 class _Scratch:

@@ -10,7 +10,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
 
-# Three tiny configurations of the architecture that differ in every size and option.
+# Four tiny configurations of the architecture that differ in every size and option.
 #   A: BASELINE config 0 (tied head, group of 2, norm weights 1).
 #   B: BASELINE config 1 (untied head, group of 3, head size decoupled from the width, prime vocabulary).
 #   C: one kv head per query head, head size 48, a window of 24 keys on every other layer.
@@ -29,6 +29,11 @@ TINY = {
                        layer_types=["full_attention", "sliding_attention", "full_attention", "sliding_attention"],
                        sliding_window=24, use_sliding_window=True),
               seed=2, norm_std=0.05),
+    # D: the head size (128) and group (2) of the Qwen3 checkpoints, which the faster bfloat16 kernels take
+    "D": dict(cfg=dict(hidden_size=192, intermediate_size=272, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=128, vocab_size=515, max_position_embeddings=640,
+                       rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True),
+              seed=3, norm_std=0.02),
 }
 # Random N(0, 0.02) weights give nearly flat attention, in which a lost key changes little. These
 # factors on the q/k norm weights and on the value/output matrices make scores a few units wide

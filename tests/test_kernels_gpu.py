@@ -150,8 +150,10 @@ class Harness:
         self.hq, self.hkv, self.hd, self.dtype, self.window = hq, hkv, hd, dtype, window
         self.cache = SequenceCache([CacheNeed(hkv, hd, window)], [None], max_tokens, dtype, "cuda", max_context=1024)
 
-    def step(self, ops, seqs, qkv, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved, scale, from_step=False):
-        """seqs: [(slot, n_new)]; qkv float32 numpy [rows, (hq + 2 hkv) * hd]. Returns attention output."""
+    def step(self, ops, seqs, qkv, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved, scale, from_step=False,
+             general=True):
+        """seqs: [(slot, n_new)]; qkv float32 numpy [rows, (hq + 2 hkv) * hd]. Returns attention output.
+        general=False lets ops.attention pick the kernel for the phase, as the model does."""
         from abacus_b200.engine.batch import Sequence, StepBatch
         ss = []
         for slot, n in seqs:
@@ -164,7 +166,13 @@ class Harness:
         kv = self.cache.views[0].kv
         ops.qkv_prep(q, self.hq, self.hkv, self.hd, batch, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved, kv)
         out = torch.full((rows + 3, self.hq * self.hd), 5.0, dtype=self.dtype, device="cuda")
-        ops.attention_generic(q, out, self.hq, self.hkv, self.hd, scale, self.window, batch, kv, from_step=from_step)
+        if general:
+            ops.attention_generic(q, out, self.hq, self.hkv, self.hd, scale, self.window, batch, kv, from_step=from_step)
+        else:
+            from abacus_b200.parts import Workspace
+            self.ws = getattr(self, "ws", None) or Workspace(torch.device("cuda", 0))
+            ops.attention(q, out, self.hq, self.hkv, self.hd, scale, self.window, batch, kv, from_step=from_step,
+                          ws=self.ws)
         for slot, n in seqs:
             self.cache.advance(slot, n)
         assert float(out[rows:].float().abs().sum()) == 0.0  # padding rows give zeros and disturb nothing
@@ -333,3 +341,33 @@ def test_gemm_tc_refuses_what_tma_cannot_address(ops):
     assert not ops.gemm_tc_takes(x, w, out)  # K = 20 is no multiple of 8: the linear layer uses the CUDA-core kernel
     with pytest.raises(ops.KernelRefused, match="multiples of 8"):
         ops.gemm_tc(x, w, out)
+
+
+@pytest.mark.parametrize("hq, hkv, hd, window", [(16, 8, 128, None), (6, 2, 64, None), (4, 4, 256, None),
+                                                 (8, 1, 64, None), (4, 2, 128, 200), (3, 1, 128, 64), (10, 2, 64, 129)])
+def test_decode_attention_split_along_the_keys(ops, hq, hkv, hd, window):
+    """Rows of very different lengths (1 key to 700: up to six chunks of 128, chunk and page edges
+    included) decoded in one step by the kernel the model uses for decode, against plain attention."""
+    rng = np.random.default_rng(hq * 100 + hd + (window or 0))
+    lens = [1, 64, 65, 128, 129, 257, 700, 383]
+    width = (hq + 2 * hkv) * hd
+    scale = 1.0 / np.sqrt(hd)
+    h = Harness(hq, hkv, hd, torch.bfloat16, window, max_tokens=64 * 40)
+    assert ops.attention_decode_takes(hq, hkv, hd, h.cache.views[0].kv)
+    data = [bf(rng.standard_normal((n, width)) * 1.5) for n in lens]
+    slots = [h.cache.open_slot() for _ in lens]
+    none = (None, None, 0.0, None, None, 0, False, scale)
+    # fill the caches with everything but the last token of each (the general kernel runs these steps)
+    for slot, d in zip(slots, data):
+        if len(d) > 1:
+            h.step(ops, [(slot, len(d) - 1)], d[:-1], *none, from_step=window is not None)
+    # the decode step: one row per sequence, plus the harness's padding rows
+    _, got = h.step(ops, [(slot, 1) for slot in slots], np.concatenate([d[-1:] for d in data]), *none, general=False)
+    for i, d in enumerate(data):
+        n = len(d)
+        q = d[:, :hq * hd].reshape(n, hq, hd)
+        k = d[:, hq * hd:(hq + hkv) * hd].reshape(n, hkv, hd)
+        v = d[:, (hq + hkv) * hd:].reshape(n, hkv, hd)
+        want = plain.attention(q, k, v, window)[-1].reshape(hq * hd)
+        np.testing.assert_allclose(got[i], want, rtol=2 ** -7, atol=2 ** -7, err_msg=f"row {i} of length {n}")
+    assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]

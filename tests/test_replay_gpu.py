@@ -68,7 +68,7 @@ def folders(tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay(folders, tmp_path, name, dtype):
     case = Case(folders[name], name, dtype)
     R, V = case.requests, case.vocab
