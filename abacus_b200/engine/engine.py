@@ -54,7 +54,10 @@ class Engine:
         self.max_context = self.cache.max_context
         model.prepare(self.max_context)
         self.vocab = spec.vocab
-        self.graphs = DecodeGraphs(self) if use_graphs else None
+        # A captured graph replays device work only: a part whose forward decides anything on the host
+        # from the step's contents cannot be captured. Parts say so with `capturable = True`.
+        capturable = all(getattr(part, "capturable", False) for b in model.blocks for part in b.parts().values())
+        self.graphs = DecodeGraphs(self) if use_graphs and capturable else None
 
     # ------------------------------------------------------------ sequences
     def open(self):

@@ -7,6 +7,7 @@ run it. The decisions of the loop (who is in which batch, who goes on, who is
 finished and why) are plain Python on the host, apart from the engine, so they
 are tested without a GPU.
 """
+import time
 from dataclasses import dataclass, field
 
 import torch
@@ -129,6 +130,9 @@ class Generator:
             while entries:
                 logits = engine.step(entries)
                 sampled = self.sampler.sample(logits, self.rng, index=engine.last_batch.seq_slot).tolist()
+                now = time.perf_counter()  # .tolist() has waited for the device
+                self.stats.setdefault("t_first_token", now)
+                self.stats["t_end"] = now
                 finished, entries = live.take(sampled)
                 for r in finished:
                     engine.close(r.slot)

@@ -45,9 +45,12 @@ class DecodeGraph:
             model.forward(self.batch, cache)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        from ..kernels import ops
+        before = ops.LAUNCHES
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.logits = model.forward(self.batch, cache)
+        self.n_kernels = ops.LAUNCHES - before  # kernels one replay runs
         self.generation = model.ws.generation
 
     def run(self, sequences):

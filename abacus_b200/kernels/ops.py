@@ -44,8 +44,13 @@ def _need_cuda(*tensors):
             raise KernelError("a kernel was given a tensor that is not on the GPU; there is no CPU path")
 
 
-def _check(lib, rc, what):
+LAUNCHES = 0  # kernels launched through this module (a captured graph's replays are not counted here)
+
+
+def _check(lib, rc, what, kernels=1):
+    global LAUNCHES
     if rc == 0:
+        LAUNCHES += kernels
         return
     if rc < 0:
         raise KernelRefused(lib.abk_last_error().decode())
@@ -231,7 +236,7 @@ def attention_decode(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, bat
         _p(qkv), _ll(row), _p(out), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _i(window or 0),
         _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(cache.k), _p(cache.v), _p(cache.page_table),
         _i(cache.table_width), _i(cache.ring_pages), _i(cache.tokens_per_page), _i(max_positions), _p(scratch),
-        _p(kernel_status(qkv.device)), _stream()), "attention_decode")
+        _p(kernel_status(qkv.device)), _stream()), "attention_decode", kernels=2)
 
 
 class _Scratch:

@@ -14,6 +14,8 @@ from .linear import Linear
 
 @MIXERS.register("attention")
 class Attention:
+    capturable = True  # its forward launches kernels only; nothing in it depends on the step's contents
+
     def __init__(self, spec):
         s = self.spec = spec
         if s.n_heads % s.n_kv_heads:

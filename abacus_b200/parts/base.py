@@ -22,6 +22,9 @@ Interfaces (duck-typed; these base classes only document them):
       cache.EntryView of this schedule entry.
   FeedForward.forward(xn, out, batch, ws)
   Position: see parts/position.py.
+  A part whose forward only launches device work (no decision on the host from the step's
+  contents, no allocation) may set `capturable = True`; decode steps of a model whose parts
+  all do are replayed as CUDA graphs. Without it the model runs step by step.
   Block.forward(x, y, batch, cache, ws) -> y': runs norms, mixer and
       feed-forward in its arrangement; y is the output still to be added to x.
 """

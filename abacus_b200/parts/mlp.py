@@ -11,6 +11,8 @@ from .linear import Linear
 
 @FEED_FORWARDS.register("gated_mlp")
 class GatedMLP:
+    capturable = True  # its forward launches kernels only; nothing in it depends on the step's contents
+
     def __init__(self, spec):
         if spec.activation != "silu":
             raise ValueError(f"activation {spec.activation!r} is not built (only silu)")

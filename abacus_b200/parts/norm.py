@@ -7,6 +7,8 @@ from .base import NORMS, to_device
 
 @NORMS.register("rmsnorm")
 class RMSNorm:
+    capturable = True  # its forward launches kernels only; nothing in it depends on the step's contents
+
     def __init__(self, spec):
         self.spec = spec
         self.weight = None
