@@ -171,11 +171,32 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
             if (flags[1] == g.splits - 1) {
                 __threadfence();
                 if (p < g.P) {
-                    for (int c = 0; c < BN && q0 + c < g.Q; c++) {
-                        float sum = 0.0f;
-                        for (int s = 0; s < g.splits; s++)
-                            sum += __ldcg(g.partials + ((long long)s * tiles + tile) * (BN * TILE_P) + c * TILE_P + row);
-                        out[(long long)p * g.stride_p + (long long)(q0 + c) * g.stride_q] = from_float<TO>(sum);
+                    const float *part = g.partials + (long long)tile * (BN * TILE_P) + row;
+                    const long long split_stride = (long long)tiles * (BN * TILE_P);
+                    const int cols = min(BN, g.Q - q0);
+                    for (int c0 = 0; c0 < cols; c0 += 8) {
+                        // eight columns at a time: all loads of a split are in flight together, and the
+                        // splits are added in order, so the sum does not depend on who came last
+                        float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                        for (int s0 = 0; s0 < g.splits; s0 += 4) {
+                            float v[4][8];
+#pragma unroll
+                            for (int i = 0; i < 4; i++)
+#pragma unroll
+                                for (int j = 0; j < 8; j++)
+                                    v[i][j] = (s0 + i < g.splits && c0 + j < cols)
+                                                  ? __ldcg(part + (s0 + i) * split_stride + (c0 + j) * TILE_P)
+                                                  : 0.0f;
+#pragma unroll
+                            for (int i = 0; i < 4; i++)
+#pragma unroll
+                                for (int j = 0; j < 8; j++) sum[j] += v[i][j];
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            if (c0 + j < cols)
+                                out[(long long)p * g.stride_p + (long long)(q0 + c0 + j) * g.stride_q] =
+                                    from_float<TO>(sum[j]);
                     }
                 }
                 if (threadIdx.x == 64) g.tickets[tile] = 0;
@@ -270,9 +291,9 @@ static int launch(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g,
 template <typename TO>
 static int launch_bn(int bn, const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g, dim3 grid, cudaStream_t s) {
     switch (bn) {
-    case 16: return launch<16, 8, TO>(mp, mq, g, grid, s);
-    case 32: return launch<32, 8, TO>(mp, mq, g, grid, s);
-    case 64: return launch<64, 6, TO>(mp, mq, g, grid, s);
+    case 16: return launch<16, 4, TO>(mp, mq, g, grid, s);  // 72 KB: three CTAs share an SM
+    case 32: return launch<32, 4, TO>(mp, mq, g, grid, s);
+    case 64: return launch<64, 4, TO>(mp, mq, g, grid, s);
     case 128: return launch<128, 3, TO>(mp, mq, g, grid, s);
     case 256: return launch<256, 2, TO>(mp, mq, g, grid, s);
     }

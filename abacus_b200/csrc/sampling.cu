@@ -55,13 +55,43 @@ __device__ __forceinline__ Best next_best(const float *row, int vocab, Best prev
     return block_best(b, scratch);
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS) argmax_kernel(const float *__restrict__ logits, long long row_stride,
-                                                                int vocab, int *__restrict__ out) {
+// The row is cut into gridDim.x slices, one block each; the last block of a row to finish (a ticket
+// in `tickets`, left at zero) picks the best of the slices. `before` is a total order, so the result
+// does not depend on which block came last.
+#define ARGMAX_SLICES 32
+#define ARGMAX_THREADS 256
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const float *__restrict__ logits, long long row_stride,
+                                                                int vocab, int *__restrict__ out, Best *part,
+                                                                int *tickets) {
     __shared__ Best scratch[33];
-    Best none;
-    none.v = 0.0f, none.i = -1;
-    Best b = next_best(logits + (long long)blockIdx.x * row_stride, vocab, none, scratch);
-    if (threadIdx.x == 0) out[blockIdx.x] = b.i;
+    __shared__ int ticket;
+    const int row = blockIdx.y, slices = gridDim.x;
+    const int per = (vocab + slices - 1) / slices, lo = blockIdx.x * per, hi = min(vocab, lo + per);
+    const float *x = logits + (long long)row * row_stride;
+    Best b;
+    b.v = -INFINITY, b.i = 0x7fffffff;
+    for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) {
+        Best c;
+        c.v = x[j], c.i = j;
+        if (before(c, b)) b = c;
+    }
+    b = block_best(b, scratch);
+    if (threadIdx.x == 0) {
+        part[(long long)row * slices + blockIdx.x] = b;
+        __threadfence();
+        ticket = atomicAdd(&tickets[row], 1);
+    }
+    __syncthreads();
+    if (ticket != slices - 1) return;
+    __threadfence();
+    Best t;
+    t.v = -INFINITY, t.i = 0x7fffffff;
+    if (threadIdx.x < slices) {
+        const volatile Best *q = part + (long long)row * slices + threadIdx.x;
+        t.v = q->v, t.i = q->i;
+    }
+    t = block_best(t, scratch);
+    if (threadIdx.x == 0) out[row] = t.i, tickets[row] = 0;
 }
 
 // Draw from the top_k logits at temperature temp: p_j = exp((l_j - l_top) / temp), the random
@@ -98,10 +128,16 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_topk_kernel(const float
     out[blockIdx.x] = chosen;
 }
 
-extern "C" int abk_argmax(const float *logits, long long row_stride, int n_rows, int vocab, int *out, void *stream) {
+// scratch: 8 * ARGMAX_SLICES * n_rows bytes; tickets: int32 [n_rows], zero before and after.
+extern "C" int abk_argmax_slices() { return ARGMAX_SLICES; }
+extern "C" int abk_argmax(const float *logits, long long row_stride, int n_rows, int vocab, int *out, void *scratch,
+                          int *tickets, void *stream) {
     if (n_rows <= 0) return 0;
     if (vocab < 1) ABK_REFUSE("argmax: vocabulary of %d", vocab);
-    argmax_kernel<<<n_rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, row_stride, vocab, out);
+    if (n_rows > 65535) ABK_REFUSE("argmax: %d rows are more than one launch takes", n_rows);
+    int slices = vocab >= 8192 ? ARGMAX_SLICES : 1;
+    argmax_kernel<<<dim3(slices, n_rows), ARGMAX_THREADS, 0, (cudaStream_t)stream>>>(logits, row_stride, vocab, out,
+                                                                                     (Best *)scratch, tickets);
     return ABK_LAUNCH_RESULT();
 }
 

@@ -1,0 +1,187 @@
+"""Times one kernel alone, at a given size, with CUDA events.
+
+    python -m abacus_b200.kernels.microbench gemm --m 8 --n 4096 --k 1024 [--out f32] [--iters 20]
+    python -m abacus_b200.kernels.microbench decode_attention --batch 8 --context 2176 --heads 16 --kv-heads 8
+    python -m abacus_b200.kernels.microbench prefill_attention --tokens 2048 --heads 16 --kv-heads 8
+    python -m abacus_b200.kernels.microbench argmax --rows 8 --vocab 151936
+    python -m abacus_b200.kernels.microbench add_rmsnorm --rows 8 --width 1024
+
+Between timed launches a buffer larger than the L2 cache is written, so every launch reads its
+operands from HBM. Prints one JSON line: the median time, and the rate of the bytes (or FLOPs)
+the operation must move at least. This is also the command to put under ncu for one kernel.
+"""
+import argparse
+import json
+import statistics
+import sys
+
+import torch
+
+
+def timed(fn, iters, flush=True):
+    scrub = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if scrub is not None:
+            scrub.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3)
+    return statistics.median(times), min(times)
+
+
+def timed_graph(fns, replays=5):
+    """Median time per launch of a captured graph that runs every function of `fns` once, back to
+    back, with no host in between. Give each function operands of its own, together larger than
+    the L2 cache, and every launch reads from HBM as in a real step."""
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for f in fns:
+            f()
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(replays):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3 / len(fns))
+    return statistics.median(times), min(times)
+
+
+def bench_gemm(args):
+    from . import ops
+    dt = torch.float32 if args.out == "f32" else torch.bfloat16
+    x = torch.randn(args.m, args.k, device="cuda").to(torch.bfloat16)
+    copies = max(2, min(64, (160 << 20) // (args.n * args.k * 2) + 1))  # weights that together exceed the L2
+    ws = [torch.randn(args.n, args.k, device="cuda").to(torch.bfloat16) for _ in range(copies)]
+    out = torch.empty(args.m, args.n, dtype=dt, device="cuda")
+    if args.with_norm:  # alternate with a small kernel, as in a model step
+        xs, wn = torch.randn(args.m, args.k, device="cuda"), torch.ones(args.k, device="cuda")
+        fns = []
+        for w in ws:
+            fns.append(lambda w=w: ops.gemm_tc(x, w, out, tile_n=args.tile_n, swap=args.swap, splits=args.splits))
+            fns.append(lambda: ops.add_rmsnorm(xs, None, wn, x, 1e-6))
+        us, best = timed_graph(fns)
+        us, best = 2 * us, 2 * best  # per pair
+    else:
+        us, best = timed_graph([lambda w=w: ops.gemm_tc(x, w, out, tile_n=args.tile_n, swap=args.swap,
+                                                        splits=args.splits) for w in ws])
+    nbytes = (args.m * args.k + args.n * args.k) * 2 + out.numel() * out.element_size()
+    flops = 2.0 * args.m * args.n * args.k
+    return {"kernel": "gemm_tc", "m": args.m, "n": args.n, "k": args.k, "us": round(us, 2), "best_us": round(best, 2),
+            "GB/s": round(nbytes / us / 1e3, 1), "TFLOP/s": round(flops / us / 1e6, 2)}
+
+
+def _attention_setup(batch, context, heads, kv_heads, head_dim, new_tokens):
+    from ..cache import CacheNeed, SequenceCache
+    from ..engine.batch import Sequence, StepBatch
+    cache = SequenceCache([CacheNeed(kv_heads, head_dim)], [None], batch * (context + 64), torch.bfloat16, "cuda",
+                          max_context=context + 64)
+    kv = cache.views[0].kv
+    kv.k.normal_()
+    kv.v.normal_()
+    seqs = []
+    for _ in range(batch):
+        slot = cache.open_slot()
+        cache.reserve(slot, context)
+        seqs.append(Sequence(slot, [0] * new_tokens, context - new_tokens, []))
+    rows = batch * new_tokens
+    b = StepBatch(rows, batch, 0, "cuda").fill(seqs)
+    qkv = torch.randn(rows, (heads + 2 * kv_heads) * head_dim, device="cuda").to(torch.bfloat16)
+    out = torch.empty(rows, heads * head_dim, dtype=torch.bfloat16, device="cuda")
+    return cache, kv, b, qkv, out
+
+
+def bench_decode_attention(args):
+    from . import ops
+    from ..parts import Workspace
+    cache, kv, b, qkv, out = _attention_setup(args.batch, args.context, args.heads, args.kv_heads, args.head_dim, 1)
+    ws = Workspace(torch.device("cuda", 0))
+    scale = args.head_dim ** -0.5
+    fn = lambda: ops.attention_decode(qkv, out, args.heads, args.kv_heads, args.head_dim, scale, None, b, kv, ws)
+    us, best = timed(fn, args.iters)
+    nbytes = args.batch * args.context * args.kv_heads * args.head_dim * 2 * 2
+    return {"kernel": "attention_decode", "batch": args.batch, "context": args.context, "us": round(us, 2),
+            "best_us": round(best, 2), "GB/s": round(nbytes / us / 1e3, 1)}
+
+
+def bench_prefill_attention(args):
+    from . import ops
+    from ..parts import Workspace
+    cache, kv, b, qkv, out = _attention_setup(args.batch, args.tokens, args.heads, args.kv_heads, args.head_dim,
+                                              args.tokens)
+    ws = Workspace(torch.device("cuda", 0))
+    scale = args.head_dim ** -0.5
+    ops.qkv_prep(qkv, args.heads, args.kv_heads, args.head_dim, b, None, None, 0.0, None, None, 0, False, kv)
+    fn = lambda: ops.attention(qkv, out, args.heads, args.kv_heads, args.head_dim, scale, None, b, kv, ws=ws)
+    us, best = timed(fn, args.iters)
+    flops = args.batch * 4.0 * args.head_dim * args.heads * args.tokens * (args.tokens + 1) / 2
+    return {"kernel": "attention (prefill)", "batch": args.batch, "tokens": args.tokens, "us": round(us, 2),
+            "best_us": round(best, 2), "TFLOP/s": round(flops / us / 1e6, 2)}
+
+
+def bench_argmax(args):
+    from . import ops
+    copies = max(2, (160 << 20) // (args.rows * args.vocab * 4) + 1)
+    logits = [torch.randn(args.rows, args.vocab, device="cuda") for _ in range(copies)]
+    out = torch.empty(args.rows, dtype=torch.int32, device="cuda")
+    us, best = timed_graph([lambda l=l: ops.argmax(l, out) for l in logits])
+    logits = logits[0]
+    return {"kernel": "argmax", "rows": args.rows, "vocab": args.vocab, "us": round(us, 2), "best_us": round(best, 2),
+            "GB/s": round(logits.numel() * 4 / us / 1e3, 1)}
+
+
+def bench_add_rmsnorm(args):
+    from . import ops
+    x, y = torch.randn(args.rows, args.width, device="cuda"), torch.randn(args.rows, args.width, device="cuda")
+    w = torch.ones(args.width, device="cuda")
+    out = torch.empty(args.rows, args.width, dtype=torch.bfloat16, device="cuda")
+    us, best = timed_graph([lambda: ops.add_rmsnorm(x, y, w, out, 1e-6)] * 50)
+    return {"kernel": "add_rmsnorm", "rows": args.rows, "width": args.width, "us": round(us, 2), "best_us": round(best, 2),
+            "GB/s": round(args.rows * args.width * 14 / us / 1e3, 1)}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention", "argmax", "add_rmsnorm"])
+    ap.add_argument("--m", type=int, default=8)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--out", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--swap", type=int, default=-1)
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=2176)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--width", type=int, default=1024)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--with-norm", action="store_true", help="gemm: alternate with an add_rmsnorm, as a model step does")
+    args = ap.parse_args(argv)
+    if args.kernel == "prefill_attention" and "--batch" not in (argv or sys.argv):
+        args.batch = 1
+    fn = {"gemm": bench_gemm, "decode_attention": bench_decode_attention, "prefill_attention": bench_prefill_attention,
+          "argmax": bench_argmax, "add_rmsnorm": bench_add_rmsnorm}[args.kernel]
+    print(json.dumps(fn(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

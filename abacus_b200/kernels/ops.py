@@ -176,8 +176,11 @@ def argmax(logits, out, n_rows=None):
     lib = load_module("sampling")
     n = logits.shape[0] if n_rows is None else n_rows
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32 and out.numel() >= n
-    _check(lib, lib.abk_argmax(_p(logits), _ll(logits.stride(0)), _i(n), _i(logits.shape[1]), _p(out), _stream()),
-           "argmax")
+    sc = _Scratch.of(logits.device)
+    if n > sc.argmax_rows:
+        raise KernelRefused(f"argmax: {n} rows are more than the scratch of {sc.argmax_rows} rows")
+    _check(lib, lib.abk_argmax(_p(logits), _ll(logits.stride(0)), _i(n), _i(logits.shape[1]), _p(out),
+                               _p(sc.argmax_part), _p(sc.argmax_tickets), _stream()), "argmax")
 
 
 def sample_topk(logits, temperature, top_k, rng_state, out, n_rows=None, rng_index=None):
@@ -250,6 +253,10 @@ class _Scratch:
         self.gemm_floats = torch.empty(lib.abk_gemm_tc_scratch_floats(), dtype=torch.float32, device=device)
         self.gemm_tickets = torch.zeros(lib.abk_gemm_tc_scratch_tickets(), dtype=torch.int32, device=device)
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.argmax_rows = 4096
+        self.argmax_part = torch.empty(self.argmax_rows * load_module("sampling").abk_argmax_slices() * 2,
+                                       dtype=torch.float32, device=device)
+        self.argmax_tickets = torch.zeros(self.argmax_rows, dtype=torch.int32, device=device)
 
     @classmethod
     def of(cls, device):
