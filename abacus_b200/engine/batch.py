@@ -88,6 +88,7 @@ class StepBatch:
         if pad_logits:
             self.n_logit_rows = self.cap_logits
         self.sequences = list(sequences)  # host view, for mixers that walk the sequences themselves
+        self._tiles_key = None
         self.max_position = max((s.start + len(s.tokens) - 1 for s in sequences), default=0)
         self.max_len_after = self.max_position + 1
         self.is_decode = all(len(s.tokens) == 1 for s in sequences)
@@ -97,6 +98,15 @@ class StepBatch:
             self._sent = torch.cuda.Event()
             self._sent.record()
         return self
+
+    def query_tiles(self, rows_per_tile=64):
+        """(sequence, first row among its new tokens) for every tile of `rows_per_tile` query rows of the
+        step, as an int32 tensor [tiles, 2] on the device: the work list of the prefill attention kernel."""
+        if getattr(self, "_tiles_key", None) != rows_per_tile:  # fill() resets it
+            pairs = [(i, r) for i, s in enumerate(self.sequences) for r in range(0, len(s.tokens), rows_per_tile)]
+            self._tiles = torch.tensor(pairs, dtype=torch.int32).reshape(-1, 2).to(self.device)
+            self._tiles_key = rows_per_tile
+        return self._tiles
 
     def advance_on_device(self):
         """Every sequence moves one position on (a decode step follows a decode step); the tokens are

@@ -60,6 +60,40 @@ def timed_graph(fns, replays=5):
     return statistics.median(times), min(times)
 
 
+def timed_graph_flushed(fn, repeats=5):
+    """Time of one launch of `fn` that finds nothing of its operands in the L2 cache, without the host's
+    launch latency: a captured graph alternates a write of 256 MB with the launch; the same graph
+    without the launches is timed too and subtracted."""
+    scrub = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    fn()
+    torch.cuda.synchronize()
+
+    def graph_of(with_fn):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(repeats):
+                scrub.zero_()
+                if with_fn:
+                    fn()
+        return g
+
+    both, alone = graph_of(True), graph_of(False)
+    results = []
+    for g in (both, alone):
+        g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3 / repeats)
+        results.append(statistics.median(times))
+    return results[0] - results[1], results[0] - results[1]
+
+
 def bench_gemm(args):
     from . import ops
     dt = torch.float32 if args.out == "f32" else torch.bfloat16
@@ -110,8 +144,9 @@ def bench_decode_attention(args):
     cache, kv, b, qkv, out = _attention_setup(args.batch, args.context, args.heads, args.kv_heads, args.head_dim, 1)
     ws = Workspace(torch.device("cuda", 0))
     scale = args.head_dim ** -0.5
-    fn = lambda: ops.attention_decode(qkv, out, args.heads, args.kv_heads, args.head_dim, scale, None, b, kv, ws)
-    us, best = timed(fn, args.iters)
+    fn = lambda: ops.attention_decode(qkv, out, args.heads, args.kv_heads, args.head_dim, scale, None, b, kv, ws,
+                                      simt=args.simt)
+    us, best = timed_graph_flushed(fn)
     nbytes = args.batch * args.context * args.kv_heads * args.head_dim * 2 * 2
     return {"kernel": "attention_decode", "batch": args.batch, "context": args.context, "us": round(us, 2),
             "best_us": round(best, 2), "GB/s": round(nbytes / us / 1e3, 1)}
@@ -126,7 +161,7 @@ def bench_prefill_attention(args):
     scale = args.head_dim ** -0.5
     ops.qkv_prep(qkv, args.heads, args.kv_heads, args.head_dim, b, None, None, 0.0, None, None, 0, False, kv)
     fn = lambda: ops.attention(qkv, out, args.heads, args.kv_heads, args.head_dim, scale, None, b, kv, ws=ws)
-    us, best = timed(fn, args.iters)
+    us, best = timed_graph_flushed(fn)
     flops = args.batch * 4.0 * args.head_dim * args.heads * args.tokens * (args.tokens + 1) / 2
     return {"kernel": "attention (prefill)", "batch": args.batch, "tokens": args.tokens, "us": round(us, 2),
             "best_us": round(best, 2), "TFLOP/s": round(flops / us / 1e6, 2)}
@@ -173,6 +208,7 @@ def main(argv=None):
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--width", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--simt", action="store_true", help="decode_attention: the CUDA-core kernel")
     ap.add_argument("--with-norm", action="store_true", help="gemm: alternate with an add_rmsnorm, as a model step does")
     args = ap.parse_args(argv)
     if args.kernel == "prefill_attention" and "--batch" not in (argv or sys.argv):

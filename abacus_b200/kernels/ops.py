@@ -206,8 +206,56 @@ def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cac
     if (batch.is_decode and not from_step and ws is not None and qkv.dtype == torch.bfloat16
             and attention_decode_takes(n_heads, n_kv_heads, head_dim, cache)):
         attention_decode(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws)
+    elif (not batch.is_decode and not from_step and not window and qkv.dtype == torch.bfloat16
+          and attention_prefill_takes(head_dim, cache)):
+        attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cache)
     else:
         attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=from_step)
+
+
+def attention_prefill_takes(head_dim, cache):
+    return head_dim in (64, 128) and cache.tokens_per_page == 64 and cache.ring_pages == 0
+
+
+def attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cache):
+    """Causal attention of whole prompts (or any several tokens per sequence) against the paged bfloat16
+    cache, on the tensor cores, tiles of 64 query rows (src/model.c:197-211). No window."""
+    _need_cuda(qkv, out)
+    lib = load_module("attention_mma")
+    n = batch.n_rows
+    row = (n_heads + 2 * n_kv_heads) * head_dim
+    assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
+    assert qkv.is_contiguous() and qkv.shape[1] == row and out.is_contiguous() and out.shape[1] == n_heads * head_dim
+    assert cache.k.is_contiguous() and cache.v.is_contiguous()
+    tiles = batch.query_tiles(64)
+    pool_rows = cache.k.shape[0] * cache.k.shape[1] * cache.k.shape[2]
+    _check(lib, lib.abk_attention_prefill(
+        _p(qkv), _ll(row), _i(n), _p(out), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _p(tiles),
+        _i(tiles.shape[0]), _p(batch.seq_start), _p(batch.seq_pos0), _p(batch.seq_len_after), _p(batch.seq_slot),
+        _p(cache.k), _p(cache.v), _ll(pool_rows), _p(cache.page_table), _i(cache.table_width),
+        _i(cache.tokens_per_page), _p(kernel_status(qkv.device)), _stream()), "attention_prefill")
+
+
+def _attention_decode_mma(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, max_positions):
+    lib = load_module("attention_mma")
+    lib.abk_attention_decode_mma_scratch_floats.restype = ctypes.c_longlong
+    n = batch.n_rows
+    row = (n_heads + 2 * n_kv_heads) * head_dim
+    assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
+    assert qkv.is_contiguous() and qkv.shape[1] == row and out.is_contiguous() and out.shape[1] == n_heads * head_dim
+    max_positions = max_positions or getattr(batch, "position_bound", None) or batch.max_len_after
+    if batch.max_len_after > max_positions:
+        raise KernelError(f"a row at position {batch.max_len_after - 1} is beyond the bound {max_positions}")
+    chunks = -(-max_positions // 128)
+    floats = lib.abk_attention_decode_mma_scratch_floats(_i(n), _i(n_heads), _i(head_dim), _i(chunks))
+    scratch = ws.get("attention_partials", (floats,), torch.float32)
+    pool_rows = cache.k.shape[0] * cache.k.shape[1] * cache.k.shape[2]
+    _check(lib, lib.abk_attention_decode_mma(
+        _p(qkv), _ll(row), _p(out), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _i(window or 0),
+        _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(cache.k), _p(cache.v), _ll(pool_rows),
+        _p(cache.page_table), _i(cache.table_width), _i(cache.ring_pages), _i(cache.tokens_per_page),
+        _i(max_positions), _p(scratch), _p(_attention_tickets(qkv.device, n * n_kv_heads)),
+        _p(kernel_status(qkv.device)), _stream()), "attention_decode_mma")
 
 
 def attention_decode_takes(n_heads, n_kv_heads, head_dim, cache):
@@ -216,13 +264,19 @@ def attention_decode_takes(n_heads, n_kv_heads, head_dim, cache):
     return head_dim in (64, 128, 256) and cache.tokens_per_page == 64 and smem <= 200 * 1024
 
 
-def attention_decode(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, max_positions=None):
+def attention_decode(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, max_positions=None,
+                     simt=False):
     """One new token per row against the paged bfloat16 cache, split along the keys (src/model.c:197-211).
 
+    Head sizes 64 and 128 with groups of up to 16 query heads run on the tensor cores (mma.sync);
+    head size 256, larger groups, or simt=True, on the CUDA cores.
     max_positions bounds every row's position + 1 (it sizes the grid and the scratch); by default
     the step's own maximum. A captured graph passes the bound it was captured for.
     """
     _need_cuda(qkv, out)
+    if not simt and head_dim in (64, 128) and n_heads // n_kv_heads <= 16:
+        return _attention_decode_mma(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws,
+                                     max_positions)
     lib = load_module("attention_decode")
     lib.abk_attention_decode_scratch_floats.restype = ctypes.c_longlong
     n = batch.n_rows
@@ -239,7 +293,8 @@ def attention_decode(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, bat
         _p(qkv), _ll(row), _p(out), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _i(window or 0),
         _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(cache.k), _p(cache.v), _p(cache.page_table),
         _i(cache.table_width), _i(cache.ring_pages), _i(cache.tokens_per_page), _i(max_positions), _p(scratch),
-        _p(kernel_status(qkv.device)), _stream()), "attention_decode", kernels=2)
+        _p(_attention_tickets(qkv.device, n * n_kv_heads)), _p(kernel_status(qkv.device)), _stream()),
+        "attention_decode")
 
 
 class _Scratch:
@@ -257,6 +312,7 @@ class _Scratch:
         self.argmax_part = torch.empty(self.argmax_rows * load_module("sampling").abk_argmax_slices() * 2,
                                        dtype=torch.float32, device=device)
         self.argmax_tickets = torch.zeros(self.argmax_rows, dtype=torch.int32, device=device)
+        self.attention_tickets = torch.zeros(1 << 18, dtype=torch.int32, device=device)
 
     @classmethod
     def of(cls, device):
@@ -264,6 +320,13 @@ class _Scratch:
         if key not in cls._of_device:
             cls._of_device[key] = cls(device)
         return cls._of_device[key]
+
+
+def _attention_tickets(device, n):
+    sc = _Scratch.of(device)
+    if n > sc.attention_tickets.numel():
+        raise KernelRefused(f"attention_decode: {n} (row, kv head) pairs are more than its {sc.attention_tickets.numel()} tickets")
+    return sc.attention_tickets
 
 
 def kernel_status(device):
