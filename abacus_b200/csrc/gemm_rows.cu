@@ -1,0 +1,122 @@
+// out[M, N] = x[M, K] . w[N, K]^T for a handful of rows (M <= 16: a decode step of a small batch),
+// where the product is nothing but streaming the weights once.
+//
+// A CTA of eight warps owns 16 output features (rows of w) over the whole of K; warp i takes every
+// eighth block of 32 columns. Each lane reads 16 consecutive bytes of a weight row straight from
+// global memory into the A fragment of a warp-level tensor-core product (mma.sync m16n8k16, the 8
+// columns being 8 tokens); x is read the same way into the B fragment, so both agree on which of
+// the 32 columns sit in which slot of the product. No shared-memory staging, no barrier in the
+// loop, no scratch memory: the eight partial tiles are added in warp order at the end, so the
+// result does not depend on timing. float32 accumulation.
+// Formula: src/model.c:299, 302, 307, 309.
+#define ABK_DEFINE_ERROR
+#include "common.cuh"
+
+#define ROWS_WARPS 8
+#define ROWS_THREADS (32 * ROWS_WARPS)
+
+__device__ __forceinline__ void mma_bf16(float *c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// A 16-byte read-only load (zeros if !ok). Written as volatile asm so that the loads of a turn stay
+// ahead of its products, in program order: all of them are in flight before the first is needed.
+__device__ __forceinline__ uint4 load16(const __nv_bfloat16 *p, bool ok) {
+    uint4 v;
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "mov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;\n\t"
+        "@q ld.global.nc.v4.b32 {%0, %1, %2, %3}, [%4];\n\t}"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+        : "l"(p), "r"((int)ok));
+    return v;
+}
+
+// NT: tiles of 8 tokens (1 or 2).
+// TILE: output features a CTA owns, 16 or 8. With 8 the upper half of the 16-row product is zero and
+// twice as many CTAs share the matrix: for matrices with too few rows to give every SM a tile of 16.
+template <int NT, int TILE, typename TO>
+__global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bfloat16 *__restrict__ x,
+                                                                 const __nv_bfloat16 *__restrict__ w, TO *__restrict__ out,
+                                                                 int M, int N, int K, long long ldx, long long ldw,
+                                                                 long long ldo) {
+    __shared__ float part[ROWS_WARPS][16][8 * NT + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
+    const int n0 = blockIdx.x * TILE;
+    const bool row_lo = n0 + r < N, row_hi = TILE == 16 && n0 + r + 8 < N;
+    const __nv_bfloat16 *w_lo = w + (long long)(n0 + r) * ldw + 8 * c, *w_hi = w_lo + 8 * ldw;
+    const __nv_bfloat16 *x0 = x + (long long)r * ldx + 8 * c, *x1 = x0 + 8 * ldx;
+    const bool tok0 = r < M, tok1 = r + 8 < M;
+    float acc[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; t++) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+    const int blocks = K / 32;
+    // several blocks of 32 columns a turn, so that eight 16-byte loads of weights are in flight per lane
+    constexpr int TURN = 4;
+    for (int kb = warp; kb < blocks; kb += TURN * ROWS_WARPS) {
+        uint4 a_lo[TURN], a_hi[TURN], b0[TURN], b1[TURN];
+#pragma unroll
+        for (int u = 0; u < TURN; u++) {
+            int k = (kb + u * ROWS_WARPS) * 32;
+            bool in = kb + u * ROWS_WARPS < blocks;
+            a_lo[u] = load16(w_lo + k, in && row_lo);
+            a_hi[u] = TILE == 16 ? load16(w_hi + k, in && row_hi) : make_uint4(0, 0, 0, 0);
+            b0[u] = load16(x0 + k, in && tok0);
+            if (NT > 1) b1[u] = load16(x1 + k, in && tok1);
+        }
+#pragma unroll
+        for (int u = 0; u < TURN; u++) {
+            mma_bf16(acc[0], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b0[u].x, b0[u].y);
+            mma_bf16(acc[0], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b0[u].z, b0[u].w);
+            if (NT > 1) {
+                mma_bf16(acc[1], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b1[u].x, b1[u].y);
+                mma_bf16(acc[1], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b1[u].z, b1[u].w);
+            }
+        }
+    }
+    // accumulator: rows r and r + 8 (features), columns 2c and 2c + 1 (tokens) of each tile
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+        part[warp][r][8 * t + 2 * c] = acc[t][0], part[warp][r][8 * t + 2 * c + 1] = acc[t][1];
+        part[warp][r + 8][8 * t + 2 * c] = acc[t][2], part[warp][r + 8][8 * t + 2 * c + 1] = acc[t][3];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < TILE * 8 * NT; i += ROWS_THREADS) {
+        int token = i / TILE, row = i % TILE;  // consecutive threads write consecutive features of a token
+        if (token < M && n0 + row < N) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int wv = 0; wv < ROWS_WARPS; wv++) sum += part[wv][row][token];
+            out[(long long)token * ldo + n0 + row] = from_float<TO>(sum);
+        }
+    }
+}
+
+// x [M, K], w [N, K] bfloat16 (row pitches ldx, ldw in elements); out [M, N] bfloat16 or float32.
+// M <= 16, K a multiple of 32, rows 16-byte aligned.
+extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dtype, int M, int N, int K, long long ldx,
+                             long long ldw, long long ldo, void *stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 16) ABK_REFUSE("gemm_rows: %d rows are more than 16", M);
+    if (K <= 0 || K % 32 || ldx % 8 || ldw % 8) ABK_REFUSE("gemm_rows: K = %d must be a multiple of 32 and the pitches of 8", K);
+    if (((uintptr_t)x | (uintptr_t)w) & 15) ABK_REFUSE("gemm_rows: operands must be 16-byte aligned");
+    const bool narrow = (N + 15) / 16 < 2 * 148;  // too few tiles of 16 for two CTAs on every SM
+    dim3 grid(narrow ? (N + 7) / 8 : (N + 15) / 16);
+    cudaStream_t s = (cudaStream_t)stream;
+    const __nv_bfloat16 *xb = (const __nv_bfloat16 *)x, *wb = (const __nv_bfloat16 *)w;
+#define ROWS_LAUNCH(NT, TILE, TO) \
+    gemm_rows_kernel<NT, TILE, TO><<<grid, ROWS_THREADS, 0, s>>>(xb, wb, (TO *)out, M, N, K, ldx, ldw, ldo)
+    if (out_dtype == ABK_BF16) {
+        if (M <= 8) { if (narrow) ROWS_LAUNCH(1, 8, __nv_bfloat16); else ROWS_LAUNCH(1, 16, __nv_bfloat16); }
+        else { if (narrow) ROWS_LAUNCH(2, 8, __nv_bfloat16); else ROWS_LAUNCH(2, 16, __nv_bfloat16); }
+    } else {
+        if (M <= 8) { if (narrow) ROWS_LAUNCH(1, 8, float); else ROWS_LAUNCH(1, 16, float); }
+        else { if (narrow) ROWS_LAUNCH(2, 8, float); else ROWS_LAUNCH(2, 16, float); }
+    }
+#undef ROWS_LAUNCH
+    return ABK_LAUNCH_RESULT();
+}

@@ -10,6 +10,8 @@ every row one position on, so that a loop can run without the host).
 A graph holds addresses: of the workspace, the cache, the rotary tables. If the workspace has
 grown since the capture (its generation changed), the graph is captured again.
 """
+import gc
+
 import torch
 
 from .batch import StepBatch
@@ -48,8 +50,16 @@ class DecodeGraph:
         from ..kernels import ops
         before = ops.LAUNCHES
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.logits = model.forward(self.batch, cache)
+        # Python's collector must not run inside the capture: if it frees an earlier engine's graphs or
+        # buffers there, the memory calls it makes invalidate the capture in progress.
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.logits = model.forward(self.batch, cache)
+        finally:
+            if collecting:
+                gc.enable()
         self.n_kernels = ops.LAUNCHES - before  # kernels one replay runs
         self.generation = model.ws.generation
 

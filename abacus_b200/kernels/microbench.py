@@ -101,7 +101,9 @@ def bench_gemm(args):
     copies = max(2, min(64, (160 << 20) // (args.n * args.k * 2) + 1))  # weights that together exceed the L2
     ws = [torch.randn(args.n, args.k, device="cuda").to(torch.bfloat16) for _ in range(copies)]
     out = torch.empty(args.m, args.n, dtype=dt, device="cuda")
-    if args.with_norm:  # alternate with a small kernel, as in a model step
+    if args.rows_kernel:
+        us, best = timed_graph([lambda w=w: ops.gemm_rows(x, w, out) for w in ws])
+    elif args.with_norm:  # alternate with a small kernel, as in a model step
         xs, wn = torch.randn(args.m, args.k, device="cuda"), torch.ones(args.k, device="cuda")
         fns = []
         for w in ws:
@@ -208,6 +210,7 @@ def main(argv=None):
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--width", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--rows-kernel", action="store_true", help="gemm: the weight-streaming kernel for m <= 16")
     ap.add_argument("--simt", action="store_true", help="decode_attention: the CUDA-core kernel")
     ap.add_argument("--with-norm", action="store_true", help="gemm: alternate with an add_rmsnorm, as a model step does")
     args = ap.parse_args(argv)

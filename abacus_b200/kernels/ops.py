@@ -170,6 +170,26 @@ def gemm_simt(x, w, out, m=None):
                                   _ll(x.stride(0)), _ll(w.stride(0)), _ll(out.stride(0)), _stream()), "gemm_simt")
 
 
+def gemm_rows_takes(x, w, out, m):
+    """Whether the weight-streaming kernel for a handful of rows takes this product."""
+    k = w.shape[1]
+    return (m <= 16 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 32 == 0
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1)
+
+
+def gemm_rows(x, w, out, m=None):
+    """out[:m] = x[:m] . w^T for m <= 16 rows: the weights stream once through warp-level tensor-core
+    products, no scratch memory (src/model.c:299 and the like)."""
+    _need_cuda(x, w, out)
+    lib = load_module("gemm_rows")
+    m = x.shape[0] if m is None else m
+    n, k = w.shape
+    assert x.shape[1] == k and out.shape[1] == n and x.shape[0] >= m and out.shape[0] >= m
+    _check(lib, lib.abk_gemm_rows(_p(x), _p(w), _p(out), _i(_dt(out)), _i(m), _i(n), _i(k), _ll(x.stride(0)),
+                                  _ll(w.stride(0)), _ll(out.stride(0)), _stream()), "gemm_rows")
+
+
 def argmax(logits, out, n_rows=None):
     """out[r] = index of the first maximum of logits[r] (src/main.c:31-36)."""
     _need_cuda(logits, out)

@@ -15,7 +15,13 @@ class Linear:
         self.out_features, self.in_features = weight.shape
 
     def forward(self, x, out, m=None):
-        if self.weight.dtype == torch.bfloat16 and ops.gemm_tc_takes(x, self.weight, out):
+        rows = x.shape[0] if m is None else m
+        # a handful of rows against a matrix too small to give every SM a tensor-memory tile without
+        # splitting K: stream the weights through warp-level products instead
+        if (self.weight.dtype == torch.bfloat16 and rows <= 16 and self.out_features <= 32768
+                and ops.gemm_rows_takes(x, self.weight, out, rows)):
+            ops.gemm_rows(x, self.weight, out, rows)
+        elif self.weight.dtype == torch.bfloat16 and ops.gemm_tc_takes(x, self.weight, out):
             ops.gemm_tc(x, self.weight, out, m)
         else:
             ops.gemm_simt(x, self.weight, out, m)

@@ -405,3 +405,22 @@ def test_prefill_attention_on_the_tensor_cores(ops, hq, hkv, hd):
         at += m
         np.testing.assert_allclose(got, want, rtol=2 ** -6, atol=2 ** -6, err_msg=f"prompt {i} of length {n}")
     assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 16, 32), (8, 4096, 1024), (3, 1000, 96), (9, 389, 160), (16, 1024, 3072),
+                                      (5, 24, 2048)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_rows(ops, m, n, k, out_dtype):
+    """The weight-streaming product for a handful of rows, at sizes that leave partial tiles of 16
+    features and of 8 tokens, and K with fewer blocks than warps."""
+    rng = np.random.default_rng(m * 7 + n + k)
+    x, w = bf(rng.standard_normal((m, k))), bf(rng.standard_normal((n, k)))
+    out = torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda")
+    xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    assert ops.gemm_rows_takes(xd, wd, out, m)
+    ops.gemm_rows(xd, wd, out)
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    tol = 1e-5 * np.sqrt(k) * 4 if out_dtype == torch.float32 else 2 ** -8 * np.abs(want).max()
+    np.testing.assert_allclose(out.float().cpu().numpy(), want, rtol=0 if out_dtype == torch.float32 else 2 ** -8, atol=tol)
+    with pytest.raises(ops.KernelRefused):
+        ops.gemm_rows(dev(bf(rng.standard_normal((17, k))), torch.bfloat16), wd, torch.empty(17, n, device="cuda"))
