@@ -24,7 +24,7 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 MODULES = ("elementwise", "gemm_simt", "gemm_tc", "attention_generic", "attention_decode", "attention_mma", "gemm_rows",
-           "sampling")
+           "sampling", "attention_decode_static")
 
 
 class KernelBuildError(RuntimeError):
@@ -64,8 +64,10 @@ def _build_dir():
 def _fingerprint(module):
     h = hashlib.sha256()
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    with open(os.path.join(CSRC, module + ".cu")) as f:
+        included = {line.split('"')[1] for line in f if line.startswith("#include \"") and line.count('"') >= 2}
     for name in sorted(os.listdir(CSRC)):
-        if name == module + ".cu" or name.endswith((".cuh", ".h")):
+        if name == module + ".cu" or name.endswith((".cuh", ".h")) or name in included:
             with open(os.path.join(CSRC, name), "rb") as f:
                 h.update(name.encode())
                 h.update(f.read())
