@@ -323,16 +323,43 @@ class _Scratch:
     _of_device = {}
 
     def __init__(self, device):
-        lib = load_module("gemm_tc")
-        lib.abk_gemm_tc_scratch_floats.restype = ctypes.c_longlong
-        self.gemm_floats = torch.empty(lib.abk_gemm_tc_scratch_floats(), dtype=torch.float32, device=device)
-        self.gemm_tickets = torch.zeros(lib.abk_gemm_tc_scratch_tickets(), dtype=torch.int32, device=device)
+        self.device = device
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
         self.argmax_rows = 4096
-        self.argmax_part = torch.empty(self.argmax_rows * load_module("sampling").abk_argmax_slices() * 2,
-                                       dtype=torch.float32, device=device)
-        self.argmax_tickets = torch.zeros(self.argmax_rows, dtype=torch.int32, device=device)
-        self.attention_tickets = torch.zeros(1 << 18, dtype=torch.int32, device=device)
+        self._made = {}
+
+    def _lazy(self, name, make):
+        # each kernel's scratch is made at that kernel's first use, so that a model loads
+        # (and compiles) only the kernel libraries it runs
+        if name not in self._made:
+            self._made[name] = make()
+        return self._made[name]
+
+    @property
+    def gemm_floats(self):
+        def make():
+            lib = load_module("gemm_tc")
+            lib.abk_gemm_tc_scratch_floats.restype = ctypes.c_longlong
+            return torch.empty(lib.abk_gemm_tc_scratch_floats(), dtype=torch.float32, device=self.device)
+        return self._lazy("gemm_floats", make)
+
+    @property
+    def gemm_tickets(self):
+        return self._lazy("gemm_tickets", lambda: torch.zeros(load_module("gemm_tc").abk_gemm_tc_scratch_tickets(),
+                                                              dtype=torch.int32, device=self.device))
+
+    @property
+    def argmax_part(self):
+        return self._lazy("argmax_part", lambda: torch.empty(
+            self.argmax_rows * load_module("sampling").abk_argmax_slices() * 2, dtype=torch.float32, device=self.device))
+
+    @property
+    def argmax_tickets(self):
+        return self._lazy("argmax_tickets", lambda: torch.zeros(self.argmax_rows, dtype=torch.int32, device=self.device))
+
+    @property
+    def attention_tickets(self):
+        return self._lazy("attention_tickets", lambda: torch.zeros(1 << 18, dtype=torch.int32, device=self.device))
 
     @classmethod
     def of(cls, device):
