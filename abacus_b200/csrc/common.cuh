@@ -25,6 +25,41 @@ extern "C" const char *abk_last_error() { return abk_error_text; }
 
 #define ABK_LAUNCH_RESULT() ((int)cudaGetLastError())
 
+// Programmatic dependent launch. A kernel that starts with pdl_wait() may be launched with
+// abk_launch(): its CTAs are then scheduled, and run whatever stands before pdl_wait(), while the
+// kernel before it in the stream is still finishing, and pdl_wait() returns once that kernel has
+// completed and its writes are visible. Nothing before pdl_wait() may read what an earlier kernel
+// writes, nor write global memory. In a step of a few hundred small kernels this hides most of the
+// launch latency of each. Kernels launched the ordinary way are unaffected by pdl_wait().
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+#ifdef __CUDACC__
+#include <cstdlib>
+#include <utility>
+static inline bool abk_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char *e = getenv("ABACUS_PDL");
+        on = !(e && e[0] == '0');
+    }
+    return on != 0;
+}
+template <typename... KArgs, typename... Args>
+static inline void abk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = abk_pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);  // the error, if any, is read by ABK_LAUNCH_RESULT
+}
+#endif
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <typename T> __device__ __forceinline__ T from_float(float v);

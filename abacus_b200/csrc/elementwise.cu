@@ -9,6 +9,7 @@
 template <typename TW>
 __global__ void embed_kernel(const int *__restrict__ tokens, const TW *__restrict__ table, float *__restrict__ x,
                              int d, int vocab, int *status) {
+    pdl_wait();
     int t = blockIdx.x;
     int tok = tokens[t];
     bool bad = tok < 0 || tok >= vocab;
@@ -24,9 +25,9 @@ extern "C" int abk_embed(const int *tokens, const void *table, int table_dtype, 
     int threads = d >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == ABK_BF16)
-        embed_kernel<<<n_tokens, threads, 0, s>>>(tokens, (const __nv_bfloat16 *)table, x, d, vocab, status);
+        abk_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, tokens, (const __nv_bfloat16 *)table, x, d, vocab, status);
     else
-        embed_kernel<<<n_tokens, threads, 0, s>>>(tokens, (const float *)table, x, d, vocab, status);
+        abk_launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, tokens, (const float *)table, x, d, vocab, status);
     return ABK_LAUNCH_RESULT();
 }
 
@@ -38,6 +39,7 @@ template <typename TO>
 __global__ void add_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ y, const float *__restrict__ w,
                                    TO *__restrict__ out, const int *__restrict__ rows, int d, float eps) {
     __shared__ float scratch[33];
+    pdl_wait();
     int r = blockIdx.x;
     long long src = rows ? rows[r] : r;
     float *xr = x + src * d;
@@ -66,9 +68,9 @@ extern "C" int abk_add_rmsnorm(float *x, const float *y, const float *w, void *o
     int threads = d >= 2048 ? 512 : d >= 512 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == ABK_BF16)
-        add_rmsnorm_kernel<<<n_rows, threads, 0, s>>>(x, y, w, (__nv_bfloat16 *)out, rows, d, eps);
+        abk_launch(add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, s, x, y, w, (__nv_bfloat16 *)out, rows, d, eps);
     else
-        add_rmsnorm_kernel<<<n_rows, threads, 0, s>>>(x, y, w, (float *)out, rows, d, eps);
+        abk_launch(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, x, y, w, (float *)out, rows, d, eps);
     return ABK_LAUNCH_RESULT();
 }
 
@@ -76,6 +78,7 @@ extern "C" int abk_add_rmsnorm(float *x, const float *y, const float *w, void *o
 // act[t, j] = silu(gate_up[t, j]) * gate_up[t, inter + j]              (src/model.c:274-282)
 template <typename T>
 __global__ void swiglu_kernel(const T *__restrict__ gate_up, T *__restrict__ act, long long total, int inter) {
+    pdl_wait();
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
          e += (long long)gridDim.x * blockDim.x) {
         long long t = e / inter;
@@ -86,17 +89,45 @@ __global__ void swiglu_kernel(const T *__restrict__ gate_up, T *__restrict__ act
     }
 }
 
+// bfloat16 with inter a multiple of 8: eight elements a thread, read and written as 16-byte vectors.
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16 *__restrict__ gate_up, __nv_bfloat16 *__restrict__ act,
+                                     long long groups, int inter) {
+    pdl_wait();
+    const int per_row = inter >> 3;
+    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += (long long)gridDim.x * blockDim.x) {
+        long long t = g / per_row;
+        int j = (int)(g - t * per_row) << 3;
+        uint4 graw = *(const uint4 *)(gate_up + t * 2 * inter + j), uraw = *(const uint4 *)(gate_up + t * 2 * inter + inter + j);
+        const __nv_bfloat162 *gp = (const __nv_bfloat162 *)&graw, *up = (const __nv_bfloat162 *)&uraw;
+        uint4 out;
+        __nv_bfloat162 *op = (__nv_bfloat162 *)&out;
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            float2 gv = __bfloat1622float2(gp[e]), uv = __bfloat1622float2(up[e]);
+            op[e] = __floats2bfloat162_rn(gv.x / (1.0f + expf(-gv.x)) * uv.x, gv.y / (1.0f + expf(-gv.y)) * uv.y);
+        }
+        *(uint4 *)(act + t * inter + j) = out;
+    }
+}
+
 extern "C" int abk_swiglu(const void *gate_up, void *act, int dtype, int n_tokens, int inter, void *stream) {
     long long total = (long long)n_tokens * inter;
     if (total <= 0) return 0;
+    if (dtype == ABK_BF16 && inter % 8 == 0 && ((uintptr_t)gate_up | (uintptr_t)act) % 16 == 0) {
+        long long groups = total >> 3, want = (groups + 255) / 256;
+        int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+        abk_launch(swiglu_bf16x8_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16 *)gate_up,
+                   (__nv_bfloat16 *)act, groups, inter);
+        return ABK_LAUNCH_RESULT();
+    }
     int threads = 256;
     long long blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == ABK_BF16)
-        swiglu_kernel<<<(int)blocks, threads, 0, s>>>((const __nv_bfloat16 *)gate_up, (__nv_bfloat16 *)act, total, inter);
+        abk_launch(swiglu_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, (const __nv_bfloat16 *)gate_up, (__nv_bfloat16 *)act, total, inter);
     else
-        swiglu_kernel<<<(int)blocks, threads, 0, s>>>((const float *)gate_up, (float *)act, total, inter);
+        abk_launch(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, (const float *)gate_up, (float *)act, total, inter);
     return ABK_LAUNCH_RESULT();
 }
 
@@ -125,6 +156,7 @@ struct QkvPrep {
 
 template <typename T> __global__ void qkv_prep_kernel(QkvPrep p) {
     __shared__ float buf[PREP_WARPS][MAX_HEAD_DIM];
+    pdl_wait();
     int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int head = blockIdx.y * PREP_WARPS + warp;
     int total_heads = p.n_heads + 2 * p.n_kv_heads;
@@ -178,6 +210,67 @@ template <typename T> __global__ void qkv_prep_kernel(QkvPrep p) {
         for (int j = lane; j < hd; j += 32) dst[j] = row[j];
 }
 
+// The same for bfloat16 heads of 64 * EPH elements that are rotated whole in half pairing (or not at
+// all): each lane owns EPH consecutive elements of the first half and their partners in the second,
+// read and written as one vector each, with no shared-memory staging.
+template <int N> struct __align__(2 * N) Bf16Pack { __nv_bfloat16 v[N]; };
+#define FAST_WARPS 8
+
+template <int EPH> __global__ void __launch_bounds__(FAST_WARPS * 32) qkv_prep_fast_kernel(QkvPrep p) {
+    constexpr int HD = 64 * EPH, HALF = 32 * EPH;
+    typedef Bf16Pack<EPH> Pack;
+    pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * FAST_WARPS + warp;
+    const int total_heads = p.n_heads + 2 * p.n_kv_heads;
+    if (head >= (p.q_only ? p.n_heads : total_heads)) return;
+    const int seq = p.token_seq[t];
+    if (seq < 0) return;
+    const int pos = p.token_pos[t];
+    __nv_bfloat16 *row = (__nv_bfloat16 *)p.qkv + ((long long)t * total_heads + head) * HD + lane * EPH;
+    const bool is_q = head < p.n_heads, is_k = !is_q && head < p.n_heads + p.n_kv_heads;
+    const int kv_head = is_q ? 0 : is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
+    Pack lo = *(const Pack *)row, hi = *(const Pack *)(row + HALF);
+    if (is_q || is_k) {
+        float a[EPH], b[EPH], ss = 0.0f;
+#pragma unroll
+        for (int e = 0; e < EPH; e++) {
+            a[e] = __bfloat162float(lo.v[e]), b[e] = __bfloat162float(hi.v[e]);
+            ss += a[e] * a[e] + b[e] * b[e];
+        }
+        const float *w = is_q ? p.q_norm : p.k_norm;
+        if (w) {
+            ss = warp_sum(ss);
+            const float scale = 1.0f / sqrtf(ss / (float)HD + p.eps);
+#pragma unroll
+            for (int e = 0; e < EPH; e++) {
+                a[e] = w[lane * EPH + e] * (a[e] * scale);
+                b[e] = w[HALF + lane * EPH + e] * (b[e] * scale);
+            }
+        }
+        if (p.cos) {
+            const float *c = p.cos + (long long)pos * HALF + lane * EPH, *s = p.sin + (long long)pos * HALF + lane * EPH;
+#pragma unroll
+            for (int e = 0; e < EPH; e++) {
+                float x = a[e], y = b[e];
+                a[e] = x * c[e] - y * s[e];
+                b[e] = y * c[e] + x * s[e];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < EPH; e++) lo.v[e] = __float2bfloat16_rn(a[e]), hi.v[e] = __float2bfloat16_rn(b[e]);
+        *(Pack *)row = lo, *(Pack *)(row + HALF) = hi;
+    }
+    if (is_q || !p.k_pool) return;
+    if (p.cache.ring_pages > 0 &&
+        pos + p.cache.ring_pages * p.cache.tokens_per_page <= p.seq_len_after[seq] - 1)
+        return;
+    const int page = cache_page(p.cache, p.seq_slot[seq], pos);
+    __nv_bfloat16 *dst = (__nv_bfloat16 *)(is_k ? p.k_pool : p.v_pool) +
+                         cache_offset(p.cache, page, kv_head, p.n_kv_heads, pos, HD) + lane * EPH;
+    *(Pack *)dst = lo, *(Pack *)(dst + HALF) = hi;
+}
+
 extern "C" int abk_qkv_prep(void *qkv, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int q_only,
                             const int *token_seq, const int *token_pos, const int *seq_slot, const int *seq_len_after,
                             const float *q_norm, const float *k_norm, float eps, const float *cos, const float *sin,
@@ -198,10 +291,18 @@ extern "C" int abk_qkv_prep(void *qkv, int dtype, int n_tokens, int n_heads, int
     int total_heads = n_heads + 2 * n_kv_heads;
     dim3 grid(n_tokens, (total_heads + PREP_WARPS - 1) / PREP_WARPS);
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == ABK_BF16 && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
+        (!cos || (rotary_dim == head_dim && !interleaved)) && (uintptr_t)qkv % 16 == 0) {
+        dim3 fast((unsigned)n_tokens, (total_heads + FAST_WARPS - 1) / FAST_WARPS);
+        if (head_dim == 64) abk_launch(qkv_prep_fast_kernel<1>, fast, dim3(FAST_WARPS * 32), 0, s, p);
+        else if (head_dim == 128) abk_launch(qkv_prep_fast_kernel<2>, fast, dim3(FAST_WARPS * 32), 0, s, p);
+        else abk_launch(qkv_prep_fast_kernel<4>, fast, dim3(FAST_WARPS * 32), 0, s, p);
+        return ABK_LAUNCH_RESULT();
+    }
     if (dtype == ABK_BF16)
-        qkv_prep_kernel<__nv_bfloat16><<<grid, PREP_WARPS * 32, 0, s>>>(p);
+        abk_launch(qkv_prep_kernel<__nv_bfloat16>, grid, dim3(PREP_WARPS * 32), 0, s, p);
     else
-        qkv_prep_kernel<float><<<grid, PREP_WARPS * 32, 0, s>>>(p);
+        abk_launch(qkv_prep_kernel<float>, grid, dim3(PREP_WARPS * 32), 0, s, p);
     return ABK_LAUNCH_RESULT();
 }
 

@@ -39,16 +39,20 @@ __device__ __forceinline__ uint4 load16(const __nv_bfloat16 *p, bool ok) {
 // NT: tiles of 8 tokens (1 or 2).
 // TILE: output features a CTA owns, 16 or 8. With 8 the upper half of the 16-row product is zero and
 // twice as many CTAs share the matrix: for matrices with too few rows to give every SM a tile of 16.
-template <int NT, int TILE, typename TO>
+// GATED: w holds N gate rows and then N up rows (src/model.c:98); a CTA owns 8 outputs, takes their gate
+// rows as the lower and their up rows as the upper half of the product, and stores silu(gate) * up
+// (src/model.c:274-282) instead of the two sums: the feed-forward's first product and its activation in one.
+template <int NT, int TILE, bool GATED, typename TO>
 __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bfloat16 *__restrict__ x,
                                                                  const __nv_bfloat16 *__restrict__ w, TO *__restrict__ out,
                                                                  int M, int N, int K, long long ldx, long long ldw,
                                                                  long long ldo) {
     __shared__ float part[ROWS_WARPS][16][8 * NT + 1];
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
     const int n0 = blockIdx.x * TILE;
-    const bool row_lo = n0 + r < N, row_hi = TILE == 16 && n0 + r + 8 < N;
-    const __nv_bfloat16 *w_lo = w + (long long)(n0 + r) * ldw + 8 * c, *w_hi = w_lo + 8 * ldw;
+    const bool row_lo = n0 + r < N, row_hi = GATED ? row_lo : TILE == 16 && n0 + r + 8 < N;
+    const __nv_bfloat16 *w_lo = w + (long long)(n0 + r) * ldw + 8 * c, *w_hi = w_lo + (GATED ? (long long)N : 8) * ldw;
     const __nv_bfloat16 *x0 = x + (long long)r * ldx + 8 * c, *x1 = x0 + 8 * ldx;
     const bool tok0 = r < M, tok1 = r + 8 < M;
     float acc[NT][4];
@@ -64,7 +68,7 @@ __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bflo
             int k = (kb + u * ROWS_WARPS) * 32;
             bool in = kb + u * ROWS_WARPS < blocks;
             a_lo[u] = load16(w_lo + k, in && row_lo);
-            a_hi[u] = TILE == 16 ? load16(w_hi + k, in && row_hi) : make_uint4(0, 0, 0, 0);
+            a_hi[u] = TILE == 16 || GATED ? load16(w_hi + k, in && row_hi) : make_uint4(0, 0, 0, 0);
             b0[u] = load16(x0 + k, in && tok0);
             if (NT > 1) b1[u] = load16(x1 + k, in && tok1);
         }
@@ -88,9 +92,17 @@ __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bflo
     for (int i = threadIdx.x; i < TILE * 8 * NT; i += ROWS_THREADS) {
         int token = i / TILE, row = i % TILE;  // consecutive threads write consecutive features of a token
         if (token < M && n0 + row < N) {
-            float sum = 0.0f;
+            float sum = 0.0f, up = 0.0f;
 #pragma unroll
             for (int wv = 0; wv < ROWS_WARPS; wv++) sum += part[wv][row][token];
+            if (GATED) {
+#pragma unroll
+                for (int wv = 0; wv < ROWS_WARPS; wv++) up += part[wv][row + 8][token];
+                // gate and up pass through bfloat16, as they do where they are stored between the product
+                // and the activation (larger steps): a token's result is the same on either way
+                sum = __bfloat162float(__float2bfloat16_rn(sum)), up = __bfloat162float(__float2bfloat16_rn(up));
+                sum = sum / (1.0f + expf(-sum)) * up;
+            }
             out[(long long)token * ldo + n0 + row] = from_float<TO>(sum);
         }
     }
@@ -109,7 +121,7 @@ extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dt
     cudaStream_t s = (cudaStream_t)stream;
     const __nv_bfloat16 *xb = (const __nv_bfloat16 *)x, *wb = (const __nv_bfloat16 *)w;
 #define ROWS_LAUNCH(NT, TILE, TO) \
-    gemm_rows_kernel<NT, TILE, TO><<<grid, ROWS_THREADS, 0, s>>>(xb, wb, (TO *)out, M, N, K, ldx, ldw, ldo)
+    abk_launch(gemm_rows_kernel<NT, TILE, false, TO>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (TO *)out, M, N, K, ldx, ldw, ldo)
     if (out_dtype == ABK_BF16) {
         if (M <= 8) { if (narrow) ROWS_LAUNCH(1, 8, __nv_bfloat16); else ROWS_LAUNCH(1, 16, __nv_bfloat16); }
         else { if (narrow) ROWS_LAUNCH(2, 8, __nv_bfloat16); else ROWS_LAUNCH(2, 16, __nv_bfloat16); }
@@ -118,5 +130,23 @@ extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dt
         else { if (narrow) ROWS_LAUNCH(2, 8, float); else ROWS_LAUNCH(2, 16, float); }
     }
 #undef ROWS_LAUNCH
+    return ABK_LAUNCH_RESULT();
+}
+
+// act[M, N] = silu(x . w_gate^T) * (x . w_up^T) where w [2 N, K] holds the gate rows and then the up rows.
+// x, w bfloat16; act bfloat16. M <= 16, K a multiple of 32.
+extern "C" int abk_gemm_rows_swiglu(const void *x, const void *w, void *act, int M, int N, int K, long long ldx,
+                                    long long ldw, long long ldo, void *stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 16) ABK_REFUSE("gemm_rows_swiglu: %d rows are more than 16", M);
+    if (K <= 0 || K % 32 || ldx % 8 || ldw % 8) ABK_REFUSE("gemm_rows_swiglu: K = %d must be a multiple of 32 and the pitches of 8", K);
+    if (((uintptr_t)x | (uintptr_t)w) & 15) ABK_REFUSE("gemm_rows_swiglu: operands must be 16-byte aligned");
+    dim3 grid((N + 7) / 8);
+    cudaStream_t s = (cudaStream_t)stream;
+    const __nv_bfloat16 *xb = (const __nv_bfloat16 *)x, *wb = (const __nv_bfloat16 *)w;
+    if (M <= 8)
+        abk_launch(gemm_rows_kernel<1, 8, true, __nv_bfloat16>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (__nv_bfloat16 *)act, M, N, K, ldx, ldw, ldo);
+    else
+        abk_launch(gemm_rows_kernel<2, 8, true, __nv_bfloat16>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (__nv_bfloat16 *)act, M, N, K, ldx, ldw, ldo);
     return ABK_LAUNCH_RESULT();
 }

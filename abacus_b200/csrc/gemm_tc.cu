@@ -92,6 +92,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = *tmem_holder;
+    pdl_wait();  // barriers, tensor memory and the tensor maps are ready; now the operands may be read
 
     if (warp == 0) {
         if (lane == 0) {
@@ -284,7 +285,7 @@ static int launch(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g,
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    kernel<<<grid, GEMM_THREADS, bytes, s>>>(mp, mq, g);
+    abk_launch(kernel, grid, dim3(GEMM_THREADS), (size_t)bytes, s, mp, mq, g);
     return ABK_LAUNCH_RESULT();
 }
 

@@ -65,6 +65,7 @@ __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const float *__r
                                                                 int *tickets) {
     __shared__ Best scratch[33];
     __shared__ int ticket;
+    pdl_wait();
     const int row = blockIdx.y, slices = gridDim.x;
     const int per = (vocab + slices - 1) / slices, lo = blockIdx.x * per, hi = min(vocab, lo + per);
     const float *x = logits + (long long)row * row_stride;
@@ -136,8 +137,8 @@ extern "C" int abk_argmax(const float *logits, long long row_stride, int n_rows,
     if (vocab < 1) ABK_REFUSE("argmax: vocabulary of %d", vocab);
     if (n_rows > 65535) ABK_REFUSE("argmax: %d rows are more than one launch takes", n_rows);
     int slices = vocab >= 8192 ? ARGMAX_SLICES : 1;
-    argmax_kernel<<<dim3(slices, n_rows), ARGMAX_THREADS, 0, (cudaStream_t)stream>>>(logits, row_stride, vocab, out,
-                                                                                     (Best *)scratch, tickets);
+    abk_launch(argmax_kernel, dim3(slices, n_rows), dim3(ARGMAX_THREADS), 0, (cudaStream_t)stream, logits, row_stride,
+               vocab, out, (Best *)scratch, tickets);
     return ABK_LAUNCH_RESULT();
 }
 

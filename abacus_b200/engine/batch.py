@@ -104,6 +104,8 @@ class StepBatch:
         step, as an int32 tensor [tiles, 2] on the device: the work list of the prefill attention kernel."""
         if getattr(self, "_tiles_key", None) != rows_per_tile:  # fill() resets it
             pairs = [(i, r) for i, s in enumerate(self.sequences) for r in range(0, len(s.tokens), rows_per_tile)]
+            # tiles that see the most keys first: the long ones start early and the short ones fill the tail
+            pairs.sort(key=lambda ir: -(self.sequences[ir[0]].start + ir[1]))
             self._tiles = torch.tensor(pairs, dtype=torch.int32).reshape(-1, 2).to(self.device)
             self._tiles_key = rows_per_tile
         return self._tiles

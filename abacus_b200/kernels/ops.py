@@ -190,6 +190,18 @@ def gemm_rows(x, w, out, m=None):
                                   _ll(w.stride(0)), _ll(out.stride(0)), _stream()), "gemm_rows")
 
 
+def gemm_rows_swiglu(x, w_gate_up, act, m=None):
+    """act[:m] = silu(x . gate^T) * (x . up^T) for m <= 16 rows, w_gate_up [2 I, K] holding the gate rows and
+    then the up rows: the feed-forward's first product and its activation in one kernel (src/model.c:307-308)."""
+    _need_cuda(x, w_gate_up, act)
+    lib = load_module("gemm_rows")
+    m = x.shape[0] if m is None else m
+    two_i, k = w_gate_up.shape
+    assert x.shape[1] == k and act.shape[1] == two_i // 2 and act.dtype == torch.bfloat16 and act.stride(1) == 1
+    _check(lib, lib.abk_gemm_rows_swiglu(_p(x), _p(w_gate_up), _p(act), _i(m), _i(two_i // 2), _i(k), _ll(x.stride(0)),
+                                         _ll(w_gate_up.stride(0)), _ll(act.stride(0)), _stream()), "gemm_rows_swiglu")
+
+
 def argmax(logits, out, n_rows=None):
     """out[r] = index of the first maximum of logits[r] (src/main.c:31-36)."""
     _need_cuda(logits, out)
@@ -257,8 +269,8 @@ def attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cac
 
 
 def _attention_decode_mma(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, max_positions):
-    lib = load_module("attention_mma")
-    lib.abk_attention_decode_mma_scratch_floats.restype = ctypes.c_longlong
+    lib = load_module("attention_decode_ring")
+    lib.abk_attention_decode_ring_scratch_floats.restype = ctypes.c_longlong
     n = batch.n_rows
     row = (n_heads + 2 * n_kv_heads) * head_dim
     assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
@@ -266,11 +278,11 @@ def _attention_decode_mma(qkv, out, n_heads, n_kv_heads, head_dim, scale, window
     max_positions = max_positions or getattr(batch, "position_bound", None) or batch.max_len_after
     if batch.max_len_after > max_positions:
         raise KernelError(f"a row at position {batch.max_len_after - 1} is beyond the bound {max_positions}")
-    chunks = -(-max_positions // 128)
-    floats = lib.abk_attention_decode_mma_scratch_floats(_i(n), _i(n_heads), _i(head_dim), _i(chunks))
+    floats = lib.abk_attention_decode_ring_scratch_floats(_i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim),
+                                                          _i(max_positions))
     scratch = ws.get("attention_partials", (floats,), torch.float32)
     pool_rows = cache.k.shape[0] * cache.k.shape[1] * cache.k.shape[2]
-    _check(lib, lib.abk_attention_decode_mma(
+    _check(lib, lib.abk_attention_decode_ring(
         _p(qkv), _ll(row), _p(out), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _i(window or 0),
         _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(cache.k), _p(cache.v), _ll(pool_rows),
         _p(cache.page_table), _i(cache.table_width), _i(cache.ring_pages), _i(cache.tokens_per_page),

@@ -29,9 +29,12 @@ class GatedMLP:
 
     def forward(self, xn, out, batch, ws):
         n, inter = batch.n_rows, self.spec.inter
-        gate_up = ws.get("gate_up", (n, 2 * inter), self.ctx.dtype)
         act = ws.get("act", (n, inter), self.ctx.dtype)
-        self.gate_up.forward(xn, gate_up, n)
-        ops.swiglu(gate_up, act)
+        if n <= 16 and ops.gemm_rows_takes(xn, self.gate_up.weight, act, n):
+            ops.gemm_rows_swiglu(xn, self.gate_up.weight, act, n)  # a handful of rows: product and activation in one
+        else:
+            gate_up = ws.get("gate_up", (n, 2 * inter), self.ctx.dtype)
+            self.gate_up.forward(xn, gate_up, n)
+            ops.swiglu(gate_up, act)
         self.down.forward(act, out, n)
         return out

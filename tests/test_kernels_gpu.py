@@ -424,3 +424,14 @@ def test_gemm_rows(ops, m, n, k, out_dtype):
     np.testing.assert_allclose(out.float().cpu().numpy(), want, rtol=0 if out_dtype == torch.float32 else 2 ** -8, atol=tol)
     with pytest.raises(ops.KernelRefused):
         ops.gemm_rows(dev(bf(rng.standard_normal((17, k))), torch.bfloat16), wd, torch.empty(17, n, device="cuda"))
+
+
+@pytest.mark.parametrize("m, inter, k", [(1, 8, 32), (8, 3072, 1024), (5, 100, 96), (16, 272, 192), (11, 40, 2048)])
+def test_gemm_rows_with_swiglu(ops, m, inter, k):
+    """The feed-forward's first product and its activation in one kernel, against product then swiglu."""
+    rng = np.random.default_rng(m + inter + k)
+    x, w = bf(rng.standard_normal((m, k))), bf(0.3 * rng.standard_normal((2 * inter, k)))
+    act = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_rows_swiglu(dev(x, torch.bfloat16), dev(w, torch.bfloat16), act)
+    want = plain.swiglu(plain.linear(x, w))
+    np.testing.assert_allclose(act.float().cpu().numpy(), want, rtol=2 ** -7, atol=2 ** -7 * np.abs(want).max())
