@@ -1,0 +1,317 @@
+// Causal prefill attention on the 5th-generation tensor cores (tcgen05), head size 128, bfloat16
+// paged cache, no window.
+//
+// A CTA takes 128 query rows of one (sequence, head) and walks the pages of keys the last of its
+// rows may see, 64 keys at a time:
+//   warp 0     TMA: the query tile once ([128, 128] as two swizzled boxes), then a page of keys and
+//              a page of values per step into a ring of three stages;
+//   warp 1     one thread issues tcgen05.mma: S = Q K^T (128 x 64, into one of two score buffers in
+//              tensor memory) and O += P V (128 x 128, P from shared memory, V as an MN-major
+//              operand straight from the page), S of the next page before O of this one, so that
+//              the softmax of page j+1 runs under the second product of page j;
+//   warps 2-5  one thread per query row: reads its row of S from tensor memory (tcgen05.ld),
+//              scales, masks (only pages that cross the diagonal), keeps the running maximum and
+//              sum in float32, writes P as bfloat16 into shared memory in the swizzled layout the
+//              tensor core reads, and, when the maximum grew, rescales its row of O in tensor
+//              memory (tcgen05.ld / tcgen05.st) between two second products.
+// Tensor memory: 2 x 64 columns of scores + 128 columns of output = 256 of 512. Every wait on an
+// mbarrier is bounded; a wait that runs out sets status word 3 and the CTA winds down.
+// Formula: src/model.c:197-211; softmax in float32, probabilities rounded to bfloat16 for P V.
+#define ABK_DEFINE_ERROR
+#include "common.cuh"
+#include "tc_common.cuh"
+#include "tensor_map.cuh"
+
+#define TQ 128        // query rows per CTA
+#define TK 64         // keys per step: one page
+#define HD 128
+#define KV_STAGES 3
+#define FA_THREADS 192
+#define Q_BYTES (TQ * HD * 2)       // two boxes of [128 rows, 64 columns]
+#define KV_BYTES (TK * HD * 2)      // two boxes of [64 rows, 64 columns]
+#define P_BYTES (TQ * TK * 2)       // one box of [128 rows, 64 columns]
+#define BOX_Q (TQ * 128)            // bytes of a query box
+#define BOX_KV (TK * 128)           // bytes of a key or value box
+
+struct AttnTc {
+    __nv_bfloat16 *out;  // [tokens, n_heads * HD]
+    int n_heads, n_kv_heads;
+    float scale_log2;
+    const int *tiles;  // [n_tiles][2]: sequence of the step, first of its 128 rows among the sequence's new tokens
+    const int *seq_start, *seq_pos0, *seq_len_after, *seq_slot;
+    PagedCache cache;
+    int *status;
+};
+
+// Shared-memory descriptor of a B operand whose N dimension is contiguous (values: [key][head_dim]),
+// stored as boxes of [rows = keys, 64 columns] with the 128-byte swizzle: 8 keys are 1024 bytes apart
+// (stride offset), the next 64 columns are `next_box` bytes on (leading offset).
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr, uint32_t next_box) {
+    uint64_t d = (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((next_box >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// K-major operand made of boxes of [rows, 64 columns]: one box per 64 of K; inside a box +32 bytes per 16 of K.
+__device__ __forceinline__ uint64_t k_major_desc(uint32_t base, uint32_t box_bytes, int k16) {
+    return tc::smem_desc_k_sw128(base + (k16 / 4) * box_bytes + (k16 % 4) * 32);
+}
+__host__ __device__ constexpr uint32_t idesc_b_mn(int m, int n) { return tc::idesc_bf16_f32(m, n) | (1u << 16); }
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__global__ void __launch_bounds__(FA_THREADS) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
+                                                                     const __grid_constant__ CUtensorMap k_map,
+                                                                     const __grid_constant__ CUtensorMap v_map, AttnTc p) {
+    extern __shared__ uint8_t fa_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)fa_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *q_s = smem, *k_s = q_s + Q_BYTES, *v_s = k_s + KV_STAGES * KV_BYTES, *p_s = v_s + KV_STAGES * KV_BYTES;
+    uint64_t *bars = (uint64_t *)(p_s + 2 * P_BYTES);
+    uint64_t *q_full = bars, *kv_full = bars + 1, *kv_empty = kv_full + KV_STAGES, *s_full = kv_empty + KV_STAGES,
+             *p_full = s_full + 2, *o_step = p_full + 2;  // o_step: the second product of a page is done
+    uint32_t *tmem_holder = (uint32_t *)(o_step + 1);
+    volatile int *failed = (volatile int *)(tmem_holder + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (*(volatile int *)(p.status + 3)) return;  // an earlier CTA gave up on a wait: do not queue up behind it
+    const int seq = p.tiles[2 * blockIdx.x], row0 = p.tiles[2 * blockIdx.x + 1], h = blockIdx.y;
+    const int kvh = h / (p.n_heads / p.n_kv_heads);
+    const int start = p.seq_start[seq], pos0 = p.seq_pos0[seq], n_new = p.seq_len_after[seq] - pos0;
+    const int last_row = min(row0 + TQ - 1, n_new - 1);
+    const int n_steps = (pos0 + last_row) / TK + 1;  // pages of keys the tile's last row sees
+
+    if (threadIdx.x == 0) {
+        *failed = 0;
+        tc::mbar_init(q_full, 1);
+        for (int s = 0; s < KV_STAGES; s++) tc::mbar_init(&kv_full[s], 1), tc::mbar_init(&kv_empty[s], 1);
+        for (int b = 0; b < 2; b++) tc::mbar_init(&s_full[b], 1), tc::mbar_init(&p_full[b], 128);
+        tc::mbar_init(o_step, 1);
+        tc::mbar_init_fence();
+        tc::tma_prefetch_map(&q_map), tc::tma_prefetch_map(&k_map), tc::tma_prefetch_map(&v_map);
+    }
+    if (warp == 1) tc::tmem_alloc(tmem_holder, 256);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem = *tmem_holder, tmem_o = tmem + 128;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tc::mbar_expect_tx(q_full, Q_BYTES);
+            tc::tma_load_2d(q_s, &q_map, h * HD, start + row0, q_full);
+            tc::tma_load_2d(q_s + BOX_Q, &q_map, h * HD + 64, start + row0, q_full);
+            const int slot = p.seq_slot[seq];
+            int issued = 0;
+            for (int j = 0; j < n_steps; j++, issued++) {
+                int s = j % KV_STAGES;
+                if (!tc::mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1)) {
+                    atomicOr(p.status + 3, 2);
+                    *failed = 1;
+                    break;
+                }
+                int y = (cache_page(p.cache, slot, j * TK) * p.n_kv_heads + kvh) * TK;
+                tc::mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
+                tc::tma_load_2d(k_s + s * KV_BYTES, &k_map, 0, y, &kv_full[s]);
+                tc::tma_load_2d(k_s + s * KV_BYTES + BOX_KV, &k_map, 64, y, &kv_full[s]);
+                tc::tma_load_2d(v_s + s * KV_BYTES, &v_map, 0, y, &kv_full[s]);
+                tc::tma_load_2d(v_s + s * KV_BYTES + BOX_KV, &v_map, 64, y, &kv_full[s]);
+            }
+            if (*failed)
+                for (int i = max(0, issued - KV_STAGES); i < issued; i++) tc::mbar_wait(&kv_full[i % KV_STAGES], (i / KV_STAGES) & 1);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = tc::idesc_bf16_f32(TQ, TK), idesc_o = idesc_b_mn(TQ, HD);
+            const uint32_t qa = tc::smem_addr(q_s);
+            bool ok = tc::mbar_wait(q_full, 0);
+            if (!ok) atomicOr(p.status + 3, 4);
+            // step j: S(j) = Q K(j)^T, then O += P(j-1) V(j-1); one more turn for the last second product
+            for (int j = 0; j <= n_steps && ok; j++) {
+                if (j < n_steps) {
+                    const int s = j % KV_STAGES, b = j & 1;
+                    ok = ok && tc::mbar_wait(&kv_full[s], (j / KV_STAGES) & 1);
+                    if (!ok) atomicOr(p.status + 3, 8);
+                    // the score buffer is free once the softmax of step j-2 has delivered its P
+                    if (ok && j >= 2) {
+                        ok = tc::mbar_wait(&p_full[b], ((j - 2) >> 1) & 1);
+                        if (!ok) atomicOr(p.status + 3, 16);
+                    }
+                    if (!ok) break;
+                    tc::fence_after_sync();
+                    const uint32_t kb = tc::smem_addr(k_s + s * KV_BYTES);
+#pragma unroll
+                    for (int k16 = 0; k16 < HD / 16; k16++)
+                        tc::mma_ss(tmem + b * TK, k_major_desc(qa, BOX_Q, k16), k_major_desc(kb, BOX_KV, k16), idesc_s, k16 > 0);
+                    tc::mma_commit(&s_full[b]);
+                }
+                if (j >= 1) {
+                    const int i = j - 1, s = i % KV_STAGES, b = i & 1;
+                    ok = tc::mbar_wait(&p_full[b], (i >> 1) & 1);  // P(i) is in shared memory, O is rescaled
+                    if (!ok) {
+                        atomicOr(p.status + 3, 32);
+                        break;
+                    }
+                    tc::fence_after_sync();
+                    const uint32_t pa = tc::smem_addr(p_s + b * P_BYTES), vb = tc::smem_addr(v_s + s * KV_BYTES);
+#pragma unroll
+                    for (int k16 = 0; k16 < TK / 16; k16++)
+                        tc::mma_ss(tmem_o, tc::smem_desc_k_sw128(pa + k16 * 32), smem_desc_mn_sw128(vb + k16 * 2048, BOX_KV),
+                                   idesc_o, i > 0 || k16 > 0);
+                    tc::mma_commit(&kv_empty[s]);  // the page's stage may be refilled
+                    tc::mma_commit(o_step);        // and the softmax warps may touch O again
+                }
+            }
+            if (!ok) *failed = 1;
+        }
+    } else {
+        const int quarter = warp & 3, r = quarter * 32 + lane;   // this thread's query row within the tile
+        const int qpos = pos0 + row0 + r;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        float m = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_steps && ok; j++) {
+            const int b = j & 1;
+            if (!tc::mbar_wait(&s_full[b], (j >> 1) & 1)) {
+                atomicOr(p.status + 3, 64);
+                ok = false;
+                break;
+            }
+            tc::fence_after_sync();
+            float s[TK];
+#pragma unroll
+            for (int c0 = 0; c0 < TK; c0 += 16) tc::tmem_ld16(tmem + lane_base + b * TK + c0, (uint32_t *)(s + c0));
+            tc::tmem_ld_wait();
+            const bool edge = j * TK + TK - 1 > pos0 + row0;  // some key of this page lies after some row of the tile
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < TK; c++) {
+                float v = s[c] * p.scale_log2;
+                if (edge && j * TK + c > qpos) v = -INFINITY;
+                s[c] = v;
+                mx = fmaxf(mx, v);
+            }
+            const float m_new = fmaxf(m, mx);
+            const float ref = m_new == -INFINITY ? 0.0f : m_new;
+            const float corr = exp2f(m - ref);
+            float sum = 0.0f;
+            uint32_t packed[TK / 2];
+#pragma unroll
+            for (int c = 0; c < TK; c += 2) {
+                float p0 = exp2f(s[c] - ref), p1 = exp2f(s[c + 1] - ref);
+                sum += p0 + p1;
+                __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
+                packed[c / 2] = *(uint32_t *)&t;
+            }
+            l = l * corr + sum;
+            // P(j) as a K-major operand: row r, 128 bytes, eight 16-byte chunks swizzled by the row
+            uint8_t *prow = p_s + b * P_BYTES + r * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++)
+                *(uint4 *)(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+            // O may be rescaled only between two second products: wait for the one of step j-1
+            if (j >= 1 && !tc::mbar_wait(o_step, (j - 1) & 1)) {
+                atomicOr(p.status + 3, 128);
+                ok = false;
+                break;
+            }
+            const bool grew = j >= 1 && m_new > m;
+            if (__any_sync(0xffffffffu, grew)) {
+                tc::fence_after_sync();
+#pragma unroll 1
+                for (int c0 = 0; c0 < HD; c0 += 16) {
+                    uint32_t v[16];
+                    tc::tmem_ld16(tmem_o + lane_base + c0, v);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 16; e++) v[e] = __float_as_uint(__uint_as_float(v[e]) * corr);
+                    tmem_st16(tmem_o + lane_base + c0, v);
+                }
+                tmem_st_wait();
+            }
+            m = m_new;
+            fence_async_smem();  // P written by this thread is visible to the tensor core
+            tc::fence_before_sync();
+            tc::mbar_arrive(&p_full[b]);
+        }
+        // the last second product, then this row of O / l goes out
+        if (ok && !tc::mbar_wait(o_step, (n_steps - 1) & 1)) {
+            atomicOr(p.status + 3, 256);
+            ok = false;
+        }
+        if (!ok) *failed = 1;
+        tc::fence_after_sync();
+        // tcgen05.ld is a whole-warp instruction: every lane reads its row, only rows of the sequence are stored
+        if (__all_sync(0xffffffffu, ok)) {
+            const bool mine = row0 + r < n_new;
+            const float inv = 1.0f / l;
+            __nv_bfloat16 *dst = p.out + ((long long)(start + row0 + r) * p.n_heads + h) * HD;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 16) {
+                uint32_t v[16], hpk[8];
+                tc::tmem_ld16(tmem_o + lane_base + c0, v);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[2 * e]) * inv, __uint_as_float(v[2 * e + 1]) * inv);
+                    hpk[e] = *(uint32_t *)&t;
+                }
+                if (mine) {
+                    *(uint4 *)(dst + c0) = make_uint4(hpk[0], hpk[1], hpk[2], hpk[3]);
+                    *(uint4 *)(dst + c0 + 8) = make_uint4(hpk[4], hpk[5], hpk[6], hpk[7]);
+                }
+            }
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (*failed && threadIdx.x == 0) atomicOr(p.status + 3, 1);
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_free(tmem, 256);
+    }
+}
+
+// qkv: the step's rows [n_rows, row_width] (q columns first); out [n_rows, n_heads * 128].
+// tiles: int32 [n_tiles, 2] on the device (sequence, first of 128 rows). No window. status word 3 is set if a wait ran out.
+extern "C" int abk_attention_prefill_tc(const void *qkv, long long row_width, int n_rows, void *out, int n_heads,
+                                        int n_kv_heads, int head_dim, float scale, const int *tiles, int n_tiles,
+                                        const int *seq_start, const int *seq_pos0, const int *seq_len_after,
+                                        const int *seq_slot, const void *k_pool, const void *v_pool, long long pool_rows,
+                                        const int *page_table, int table_width, int tokens_per_page, int *status,
+                                        void *stream) {
+    if (n_tiles <= 0) return 0;
+    if (head_dim != HD) ABK_REFUSE("attention_prefill_tc: head_dim %d is not %d", head_dim, HD);
+    if (tokens_per_page != TK) ABK_REFUSE("attention_prefill_tc: pages of %d tokens, not %d", tokens_per_page, TK);
+    if (n_kv_heads < 1 || n_heads % n_kv_heads || n_heads > 65535) ABK_REFUSE("attention_prefill_tc: %d heads, %d kv heads", n_heads, n_kv_heads);
+    if ((uintptr_t)out % 16 || (n_heads * HD * 2) % 16) ABK_REFUSE("attention_prefill_tc: the output must be 16-byte aligned");
+    CUtensorMap qm, km, vm;
+    int rc = tmap::bf16_rows_of_128_bytes(qkv, n_rows, row_width, row_width, TQ, &qm);
+    if (!rc) rc = tmap::bf16_rows_of_128_bytes(k_pool, pool_rows, HD, HD, TK, &km);
+    if (!rc) rc = tmap::bf16_rows_of_128_bytes(v_pool, pool_rows, HD, HD, TK, &vm);
+    if (rc) return rc;
+    AttnTc p;
+    p.out = (__nv_bfloat16 *)out, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
+    p.scale_log2 = scale * 1.4426950408889634f, p.tiles = tiles, p.seq_start = seq_start, p.seq_pos0 = seq_pos0;
+    p.seq_len_after = seq_len_after, p.seq_slot = seq_slot, p.status = status;
+    p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = 0;
+    p.cache.tokens_per_page = tokens_per_page;
+    const int smem = Q_BYTES + 2 * KV_STAGES * KV_BYTES + 2 * P_BYTES + 1024 + 256;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    attn_prefill_tc_kernel<<<dim3(n_tiles, n_heads), FA_THREADS, smem, (cudaStream_t)stream>>>(qm, km, vm, p);
+    return ABK_LAUNCH_RESULT();
+}

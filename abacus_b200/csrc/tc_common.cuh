@@ -36,13 +36,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// Waits for the phase with the given parity; false if it did not come within the limit
-// (each try already blocks for a while in hardware, so the limit is seconds, not microseconds).
-#define TC_WAIT_LIMIT (1u << 22)
+// Waits for the phase with the given parity; false if it did not come within TC_WAIT_NS of wall
+// time (a quarter of a second: thousands of times longer than any wait of a working kernel, and
+// short enough that a kernel whose barriers are wrong ends at once instead of spinning for minutes).
+#define TC_WAIT_NS 250000000ull
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    for (uint32_t i = 0; i < TC_WAIT_LIMIT; i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_ns() - start > TC_WAIT_NS) return false;
+    }
 }
 
 // ------------------------------------------------------------------ TMA

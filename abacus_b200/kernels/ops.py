@@ -245,6 +245,9 @@ def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cac
         attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=from_step)
 
 
+PREFILL_ON_MMA = False  # True: head size 128 too runs on the warp-level kernel (for comparison)
+
+
 def attention_prefill_takes(head_dim, cache):
     return head_dim in (64, 128) and cache.tokens_per_page == 64 and cache.ring_pages == 0
 
@@ -259,8 +262,17 @@ def attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cac
     assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
     assert qkv.is_contiguous() and qkv.shape[1] == row and out.is_contiguous() and out.shape[1] == n_heads * head_dim
     assert cache.k.is_contiguous() and cache.v.is_contiguous()
-    tiles = batch.query_tiles(64)
     pool_rows = cache.k.shape[0] * cache.k.shape[1] * cache.k.shape[2]
+    if head_dim == 128 and not PREFILL_ON_MMA:  # tcgen05: tiles of 128 query rows, scores and output in tensor memory
+        lib = load_module("attention_tc")
+        tiles = batch.query_tiles(128)
+        _check(lib, lib.abk_attention_prefill_tc(
+            _p(qkv), _ll(row), _i(n), _p(out), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _p(tiles),
+            _i(tiles.shape[0]), _p(batch.seq_start), _p(batch.seq_pos0), _p(batch.seq_len_after), _p(batch.seq_slot),
+            _p(cache.k), _p(cache.v), _ll(pool_rows), _p(cache.page_table), _i(cache.table_width),
+            _i(cache.tokens_per_page), _p(kernel_status(qkv.device)), _stream()), "attention_prefill_tc")
+        return
+    tiles = batch.query_tiles(64)
     _check(lib, lib.abk_attention_prefill(
         _p(qkv), _ll(row), _i(n), _p(out), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _p(tiles),
         _i(tiles.shape[0]), _p(batch.seq_start), _p(batch.seq_pos0), _p(batch.seq_len_after), _p(batch.seq_slot),
