@@ -12,8 +12,8 @@
 //   warps 2-5  one thread per query row: reads its row of S from tensor memory (tcgen05.ld),
 //              scales, masks (only pages that cross the diagonal), keeps the running maximum and
 //              sum in float32, writes P as bfloat16 into shared memory in the swizzled layout the
-//              tensor core reads, and, when the maximum grew, rescales its row of O in tensor
-//              memory (tcgen05.ld / tcgen05.st) between two second products.
+//              tensor core reads, and, when the maximum has outgrown its reference by 2^8, rescales its
+//              row of O in tensor memory (tcgen05.ld / tcgen05.st) between two second products.
 // Tensor memory: 2 x 64 columns of scores + 128 columns of output = 256 of 512. Every wait on an
 // mbarrier is bounded; a wait that runs out sets status word 3 and the CTA winds down.
 // Formula: src/model.c:197-211; softmax in float32, probabilities rounded to bfloat16 for P V.
@@ -25,7 +25,7 @@
 #define TQ 128        // query rows per CTA
 #define TK 64         // keys per step: one page
 #define HD 128
-#define KV_STAGES 3
+#define KV_STAGES 2   // with the query tile and one P tile: 112 KB, two CTAs to an SM
 #define FA_THREADS 192
 #define Q_BYTES (TQ * HD * 2)       // two boxes of [128 rows, 64 columns]
 #define KV_BYTES (TK * HD * 2)      // two boxes of [64 rows, 64 columns]
@@ -67,16 +67,21 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *v) {
         "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
         : "memory");
 }
+// 2^x by the special-function unit alone (arguments here are at most 8; -inf gives 0).
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __global__ void __launch_bounds__(FA_THREADS) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                                                                      const __grid_constant__ CUtensorMap k_map,
                                                                      const __grid_constant__ CUtensorMap v_map, AttnTc p) {
-    extern __shared__ uint8_t fa_raw[];
-    uint8_t *smem = (uint8_t *)(((uintptr_t)fa_raw + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) uint8_t smem[];  // the kernel has no static shared memory: this starts aligned
     uint8_t *q_s = smem, *k_s = q_s + Q_BYTES, *v_s = k_s + KV_STAGES * KV_BYTES, *p_s = v_s + KV_STAGES * KV_BYTES;
-    uint64_t *bars = (uint64_t *)(p_s + 2 * P_BYTES);
+    uint64_t *bars = (uint64_t *)(p_s + P_BYTES);
     uint64_t *q_full = bars, *kv_full = bars + 1, *kv_empty = kv_full + KV_STAGES, *s_full = kv_empty + KV_STAGES,
              *p_full = s_full + 2, *o_step = p_full + 2;  // o_step: the second product of a page is done
     uint32_t *tmem_holder = (uint32_t *)(o_step + 1);
@@ -162,7 +167,7 @@ __global__ void __launch_bounds__(FA_THREADS) attn_prefill_tc_kernel(const __gri
                         break;
                     }
                     tc::fence_after_sync();
-                    const uint32_t pa = tc::smem_addr(p_s + b * P_BYTES), vb = tc::smem_addr(v_s + s * KV_BYTES);
+                    const uint32_t pa = tc::smem_addr(p_s), vb = tc::smem_addr(v_s + s * KV_BYTES);
 #pragma unroll
                     for (int k16 = 0; k16 < TK / 16; k16++)
                         tc::mma_ss(tmem_o, tc::smem_desc_k_sw128(pa + k16 * 32), smem_desc_mn_sw128(vb + k16 * 2048, BOX_KV),
@@ -192,40 +197,46 @@ __global__ void __launch_bounds__(FA_THREADS) attn_prefill_tc_kernel(const __gri
             for (int c0 = 0; c0 < TK; c0 += 16) tc::tmem_ld16(tmem + lane_base + b * TK + c0, (uint32_t *)(s + c0));
             tc::tmem_ld_wait();
             const bool edge = j * TK + TK - 1 > pos0 + row0;  // some key of this page lies after some row of the tile
-            float mx = -INFINITY;
+            float mx = -INFINITY;  // of the raw scores; the scale (positive) is applied to the maximum
+            if (edge) {
 #pragma unroll
-            for (int c = 0; c < TK; c++) {
-                float v = s[c] * p.scale_log2;
-                if (edge && j * TK + c > qpos) v = -INFINITY;
-                s[c] = v;
-                mx = fmaxf(mx, v);
+                for (int c = 0; c < TK; c++)
+                    if (j * TK + c > qpos) s[c] = -INFINITY;
             }
-            const float m_new = fmaxf(m, mx);
+#pragma unroll
+            for (int c = 0; c < TK; c++) mx = fmaxf(mx, s[c]);
+            mx *= p.scale_log2;
+            // `m` is the reference the row's exponentials, its sum and its O are scaled by. It follows the
+            // true maximum only when that has outgrown it by 2^8 (the probabilities stay below 256, well
+            // inside bfloat16 and float32), so that O is rescaled on a few early steps only; the final
+            // O / l does not depend on the reference.
+            const float cand = fmaxf(m, mx);
+            const bool move = __any_sync(0xffffffffu, cand > m + 8.0f);  // the first step: m is -inf
+            const float m_new = move ? cand : m;
             const float ref = m_new == -INFINITY ? 0.0f : m_new;
             const float corr = exp2f(m - ref);
             float sum = 0.0f;
             uint32_t packed[TK / 2];
 #pragma unroll
             for (int c = 0; c < TK; c += 2) {
-                float p0 = exp2f(s[c] - ref), p1 = exp2f(s[c + 1] - ref);
+                float p0 = ex2(fmaf(s[c], p.scale_log2, -ref)), p1 = ex2(fmaf(s[c + 1], p.scale_log2, -ref));
                 sum += p0 + p1;
                 __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
                 packed[c / 2] = *(uint32_t *)&t;
             }
             l = l * corr + sum;
-            // P(j) as a K-major operand: row r, 128 bytes, eight 16-byte chunks swizzled by the row
-            uint8_t *prow = p_s + b * P_BYTES + r * 128;
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++)
-                *(uint4 *)(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
-            // O may be rescaled only between two second products: wait for the one of step j-1
+            // P's tile and O may be touched only between two second products: wait for the one of step j-1
             if (j >= 1 && !tc::mbar_wait(o_step, (j - 1) & 1)) {
                 atomicOr(p.status + 3, 128);
                 ok = false;
                 break;
             }
-            const bool grew = j >= 1 && m_new > m;
-            if (__any_sync(0xffffffffu, grew)) {
+            // P(j) as a K-major operand: row r, 128 bytes, eight 16-byte chunks swizzled by the row
+            uint8_t *prow = p_s + r * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++)
+                *(uint4 *)(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+            if (j >= 1 && move) {
                 tc::fence_after_sync();
 #pragma unroll 1
                 for (int c0 = 0; c0 < HD; c0 += 16) {
@@ -305,7 +316,7 @@ extern "C" int abk_attention_prefill_tc(const void *qkv, long long row_width, in
     p.seq_len_after = seq_len_after, p.seq_slot = seq_slot, p.status = status;
     p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = 0;
     p.cache.tokens_per_page = tokens_per_page;
-    const int smem = Q_BYTES + 2 * KV_STAGES * KV_BYTES + 2 * P_BYTES + 1024 + 256;
+    const int smem = Q_BYTES + 2 * KV_STAGES * KV_BYTES + P_BYTES + 256;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
