@@ -36,7 +36,7 @@ __device__ __forceinline__ uint4 load16(const __nv_bfloat16 *p, bool ok) {
     return v;
 }
 
-// NT: tiles of 8 tokens (1 or 2).
+// NT: tiles of 8 tokens (1, 2, 4 or 8: up to 64 rows; every CTA reads all of x, which stays in the L2).
 // TILE: output features a CTA owns, 16 or 8. With 8 the upper half of the 16-row product is zero and
 // twice as many CTAs share the matrix: for matrices with too few rows to give every SM a tile of 16.
 // GATED: w holds N gate rows and then N up rows (src/model.c:98); a CTA owns 8 outputs, takes their gate
@@ -53,32 +53,30 @@ __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bflo
     const int n0 = blockIdx.x * TILE;
     const bool row_lo = n0 + r < N, row_hi = GATED ? row_lo : TILE == 16 && n0 + r + 8 < N;
     const __nv_bfloat16 *w_lo = w + (long long)(n0 + r) * ldw + 8 * c, *w_hi = w_lo + (GATED ? (long long)N : 8) * ldw;
-    const __nv_bfloat16 *x0 = x + (long long)r * ldx + 8 * c, *x1 = x0 + 8 * ldx;
-    const bool tok0 = r < M, tok1 = r + 8 < M;
+    const __nv_bfloat16 *x0 = x + (long long)r * ldx + 8 * c;  // token r of tile t is 8 t rows further
     float acc[NT][4];
 #pragma unroll
     for (int t = 0; t < NT; t++) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
     const int blocks = K / 32;
     // several blocks of 32 columns a turn, so that eight 16-byte loads of weights are in flight per lane
-    constexpr int TURN = 4;
+    constexpr int TURN = NT <= 2 ? 4 : 2;
     for (int kb = warp; kb < blocks; kb += TURN * ROWS_WARPS) {
-        uint4 a_lo[TURN], a_hi[TURN], b0[TURN], b1[TURN];
+        uint4 a_lo[TURN], a_hi[TURN], b[TURN][NT];
 #pragma unroll
         for (int u = 0; u < TURN; u++) {
             int k = (kb + u * ROWS_WARPS) * 32;
             bool in = kb + u * ROWS_WARPS < blocks;
             a_lo[u] = load16(w_lo + k, in && row_lo);
             a_hi[u] = TILE == 16 || GATED ? load16(w_hi + k, in && row_hi) : make_uint4(0, 0, 0, 0);
-            b0[u] = load16(x0 + k, in && tok0);
-            if (NT > 1) b1[u] = load16(x1 + k, in && tok1);
+#pragma unroll
+            for (int t = 0; t < NT; t++) b[u][t] = load16(x0 + (long long)(8 * t) * ldx + k, in && 8 * t + r < M);
         }
 #pragma unroll
         for (int u = 0; u < TURN; u++) {
-            mma_bf16(acc[0], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b0[u].x, b0[u].y);
-            mma_bf16(acc[0], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b0[u].z, b0[u].w);
-            if (NT > 1) {
-                mma_bf16(acc[1], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b1[u].x, b1[u].y);
-                mma_bf16(acc[1], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b1[u].z, b1[u].w);
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
+                mma_bf16(acc[t], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b[u][t].x, b[u][t].y);
+                mma_bf16(acc[t], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b[u][t].z, b[u][t].w);
             }
         }
     }
@@ -113,7 +111,7 @@ __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bflo
 extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dtype, int M, int N, int K, long long ldx,
                              long long ldw, long long ldo, void *stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > 16) ABK_REFUSE("gemm_rows: %d rows are more than 16", M);
+    if (M > 64) ABK_REFUSE("gemm_rows: %d rows are more than 64", M);
     if (K <= 0 || K % 32 || ldx % 8 || ldw % 8) ABK_REFUSE("gemm_rows: K = %d must be a multiple of 32 and the pitches of 8", K);
     if (((uintptr_t)x | (uintptr_t)w) & 15) ABK_REFUSE("gemm_rows: operands must be 16-byte aligned");
     const bool narrow = (N + 15) / 16 < 2 * 148;  // too few tiles of 16 for two CTAs on every SM
@@ -122,13 +120,13 @@ extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dt
     const __nv_bfloat16 *xb = (const __nv_bfloat16 *)x, *wb = (const __nv_bfloat16 *)w;
 #define ROWS_LAUNCH(NT, TILE, TO) \
     abk_launch(gemm_rows_kernel<NT, TILE, false, TO>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (TO *)out, M, N, K, ldx, ldw, ldo)
-    if (out_dtype == ABK_BF16) {
-        if (M <= 8) { if (narrow) ROWS_LAUNCH(1, 8, __nv_bfloat16); else ROWS_LAUNCH(1, 16, __nv_bfloat16); }
-        else { if (narrow) ROWS_LAUNCH(2, 8, __nv_bfloat16); else ROWS_LAUNCH(2, 16, __nv_bfloat16); }
-    } else {
-        if (M <= 8) { if (narrow) ROWS_LAUNCH(1, 8, float); else ROWS_LAUNCH(1, 16, float); }
-        else { if (narrow) ROWS_LAUNCH(2, 8, float); else ROWS_LAUNCH(2, 16, float); }
-    }
+#define ROWS_BY_M(TO)                                                                     \
+    if (M <= 8) { if (narrow) ROWS_LAUNCH(1, 8, TO); else ROWS_LAUNCH(1, 16, TO); }       \
+    else if (M <= 16) { if (narrow) ROWS_LAUNCH(2, 8, TO); else ROWS_LAUNCH(2, 16, TO); } \
+    else if (M <= 32) { if (narrow) ROWS_LAUNCH(4, 8, TO); else ROWS_LAUNCH(4, 16, TO); } \
+    else { if (narrow) ROWS_LAUNCH(8, 8, TO); else ROWS_LAUNCH(8, 16, TO); }
+    if (out_dtype == ABK_BF16) { ROWS_BY_M(__nv_bfloat16) } else { ROWS_BY_M(float) }
+#undef ROWS_BY_M
 #undef ROWS_LAUNCH
     return ABK_LAUNCH_RESULT();
 }
@@ -138,15 +136,18 @@ extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dt
 extern "C" int abk_gemm_rows_swiglu(const void *x, const void *w, void *act, int M, int N, int K, long long ldx,
                                     long long ldw, long long ldo, void *stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > 16) ABK_REFUSE("gemm_rows_swiglu: %d rows are more than 16", M);
+    if (M > 64) ABK_REFUSE("gemm_rows_swiglu: %d rows are more than 64", M);
     if (K <= 0 || K % 32 || ldx % 8 || ldw % 8) ABK_REFUSE("gemm_rows_swiglu: K = %d must be a multiple of 32 and the pitches of 8", K);
     if (((uintptr_t)x | (uintptr_t)w) & 15) ABK_REFUSE("gemm_rows_swiglu: operands must be 16-byte aligned");
     dim3 grid((N + 7) / 8);
     cudaStream_t s = (cudaStream_t)stream;
     const __nv_bfloat16 *xb = (const __nv_bfloat16 *)x, *wb = (const __nv_bfloat16 *)w;
-    if (M <= 8)
-        abk_launch(gemm_rows_kernel<1, 8, true, __nv_bfloat16>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (__nv_bfloat16 *)act, M, N, K, ldx, ldw, ldo);
-    else
-        abk_launch(gemm_rows_kernel<2, 8, true, __nv_bfloat16>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (__nv_bfloat16 *)act, M, N, K, ldx, ldw, ldo);
+#define GATED_LAUNCH(NT) \
+    abk_launch(gemm_rows_kernel<NT, 8, true, __nv_bfloat16>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (__nv_bfloat16 *)act, M, N, K, ldx, ldw, ldo)
+    if (M <= 8) GATED_LAUNCH(1);
+    else if (M <= 16) GATED_LAUNCH(2);
+    else if (M <= 32) GATED_LAUNCH(4);
+    else GATED_LAUNCH(8);
+#undef GATED_LAUNCH
     return ABK_LAUNCH_RESULT();
 }

@@ -173,7 +173,7 @@ def gemm_simt(x, w, out, m=None):
 def gemm_rows_takes(x, w, out, m):
     """Whether the weight-streaming kernel for a handful of rows takes this product."""
     k = w.shape[1]
-    return (m <= 16 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 32 == 0
+    return (m <= 64 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 32 == 0
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
             and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1)
 

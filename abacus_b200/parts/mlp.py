@@ -6,7 +6,7 @@ import torch
 
 from ..kernels import ops
 from .base import FEED_FORWARDS, to_device
-from .linear import Linear
+from .linear import ROWS_KERNEL_UP_TO, Linear
 
 
 @FEED_FORWARDS.register("gated_mlp")
@@ -30,7 +30,7 @@ class GatedMLP:
     def forward(self, xn, out, batch, ws):
         n, inter = batch.n_rows, self.spec.inter
         act = ws.get("act", (n, inter), self.ctx.dtype)
-        if n <= 16 and ops.gemm_rows_takes(xn, self.gate_up.weight, act, n):
+        if n <= ROWS_KERNEL_UP_TO and ops.gemm_rows_takes(xn, self.gate_up.weight, act, n):
             ops.gemm_rows_swiglu(xn, self.gate_up.weight, act, n)  # a handful of rows: product and activation in one
         else:
             gate_up = ws.get("gate_up", (n, 2 * inter), self.ctx.dtype)

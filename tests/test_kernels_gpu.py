@@ -408,7 +408,7 @@ def test_prefill_attention_on_the_tensor_cores(ops, hq, hkv, hd):
 
 
 @pytest.mark.parametrize("m, n, k", [(1, 16, 32), (8, 4096, 1024), (3, 1000, 96), (9, 389, 160), (16, 1024, 3072),
-                                      (5, 24, 2048)])
+                                      (5, 24, 2048), (17, 520, 64), (33, 72, 1024), (64, 6144, 1024), (50, 1024, 3072)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_rows(ops, m, n, k, out_dtype):
     """The weight-streaming product for a handful of rows, at sizes that leave partial tiles of 16
@@ -423,10 +423,11 @@ def test_gemm_rows(ops, m, n, k, out_dtype):
     tol = 1e-5 * np.sqrt(k) * 4 if out_dtype == torch.float32 else 2 ** -8 * np.abs(want).max()
     np.testing.assert_allclose(out.float().cpu().numpy(), want, rtol=0 if out_dtype == torch.float32 else 2 ** -8, atol=tol)
     with pytest.raises(ops.KernelRefused):
-        ops.gemm_rows(dev(bf(rng.standard_normal((17, k))), torch.bfloat16), wd, torch.empty(17, n, device="cuda"))
+        ops.gemm_rows(dev(bf(rng.standard_normal((65, k))), torch.bfloat16), wd, torch.empty(65, n, device="cuda"))
 
 
-@pytest.mark.parametrize("m, inter, k", [(1, 8, 32), (8, 3072, 1024), (5, 100, 96), (16, 272, 192), (11, 40, 2048)])
+@pytest.mark.parametrize("m, inter, k", [(1, 8, 32), (8, 3072, 1024), (5, 100, 96), (16, 272, 192), (11, 40, 2048),
+                                         (64, 3072, 1024), (29, 104, 96)])
 def test_gemm_rows_with_swiglu(ops, m, inter, k):
     """The feed-forward's first product and its activation in one kernel, against product then swiglu."""
     rng = np.random.default_rng(m + inter + k)
