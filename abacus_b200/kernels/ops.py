@@ -282,7 +282,6 @@ def attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cac
 
 def _attention_decode_mma(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, max_positions):
     lib = load_module("attention_decode_ring")
-    lib.abk_attention_decode_ring_scratch_floats.restype = ctypes.c_longlong
     n = batch.n_rows
     row = (n_heads + 2 * n_kv_heads) * head_dim
     assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
@@ -290,16 +289,12 @@ def _attention_decode_mma(qkv, out, n_heads, n_kv_heads, head_dim, scale, window
     max_positions = max_positions or getattr(batch, "position_bound", None) or batch.max_len_after
     if batch.max_len_after > max_positions:
         raise KernelError(f"a row at position {batch.max_len_after - 1} is beyond the bound {max_positions}")
-    floats = lib.abk_attention_decode_ring_scratch_floats(_i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim),
-                                                          _i(max_positions))
-    scratch = ws.get("attention_partials", (floats,), torch.float32)
     pool_rows = cache.k.shape[0] * cache.k.shape[1] * cache.k.shape[2]
     _check(lib, lib.abk_attention_decode_ring(
         _p(qkv), _ll(row), _p(out), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _i(window or 0),
         _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(cache.k), _p(cache.v), _ll(pool_rows),
         _p(cache.page_table), _i(cache.table_width), _i(cache.ring_pages), _i(cache.tokens_per_page),
-        _i(max_positions), _p(scratch), _p(_attention_tickets(qkv.device, n * n_kv_heads)),
-        _p(kernel_status(qkv.device)), _stream()), "attention_decode_mma")
+        _i(max_positions), _p(kernel_status(qkv.device)), _stream()), "attention_decode_mma")
 
 
 def attention_decode_takes(n_heads, n_kv_heads, head_dim, cache):
