@@ -28,12 +28,55 @@ extern "C" const char *abk_last_error() { return abk_error_text; }
 // Programmatic dependent launch. A kernel that starts with pdl_wait() may be launched with
 // abk_launch(): its CTAs are then scheduled, and run whatever stands before pdl_wait(), while the
 // kernel before it in the stream is still finishing, and pdl_wait() returns once that kernel has
-// completed and its writes are visible. Nothing before pdl_wait() may read what an earlier kernel
-// writes, nor write global memory. In a step of a few hundred small kernels this hides most of the
+// completed and its writes are visible. Nothing before pdl_wait() may read what the kernel just before
+// writes (what kernels further back wrote is complete by then), nor write global memory. In a step of a few hundred small kernels this hides most of the
 // launch latency of each. Kernels launched the ordinary way are unaffected by pdl_wait().
+//
+// Built with -DABK_TRACE=<number of the source file> (see kernels/trace.py), thread 0 of the first CTA
+// of every launch also records when it reached pdl_wait() and when it was let go, on the device-wide
+// nanosecond timer: the second time of a launch is the moment the launch before it had finished, so a
+// step's records give its timeline without a profiler serialising it.
+#ifdef ABK_TRACE
+#define ABK_TRACE_MAX 16384
+struct AbkTraceRecord {
+    unsigned long long reached, released;
+    int file, grid, block, pad;
+};
+__device__ AbkTraceRecord abk_trace_records[ABK_TRACE_MAX];
+__device__ unsigned int abk_trace_count;
+__device__ __forceinline__ unsigned long long abk_trace_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#ifdef ABK_DEFINE_ERROR
+// Copies the records made so far to `out` (room for `max`) and starts over; returns how many there were.
+extern "C" int abk_trace_read(void *out, int max) {
+    unsigned int n = 0, zero = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&n, abk_trace_count, sizeof n) != cudaSuccess) return -1;
+    if (n > ABK_TRACE_MAX) n = ABK_TRACE_MAX;
+    if ((int)n > max) n = max;
+    if (n && cudaMemcpyFromSymbol(out, abk_trace_records, n * sizeof(AbkTraceRecord)) != cudaSuccess) return -1;
+    if (cudaMemcpyToSymbol(abk_trace_count, &zero, sizeof zero) != cudaSuccess) return -1;
+    return (int)n;
+}
+#endif
+#endif
 __device__ __forceinline__ void pdl_wait() {
+#ifdef ABK_TRACE
+    const unsigned long long reached = abk_trace_ns();
+#endif
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#ifdef ABK_TRACE
+    if (threadIdx.x == 0 && threadIdx.y == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        unsigned int i = atomicAdd(&abk_trace_count, 1u);
+        if (i < ABK_TRACE_MAX)
+            abk_trace_records[i] = {reached, abk_trace_ns(), ABK_TRACE, (int)(gridDim.x * gridDim.y * gridDim.z),
+                                    (int)(blockDim.x * blockDim.y), 0};
+    }
+#endif
 }
 
 #ifdef __CUDACC__
@@ -47,16 +90,31 @@ static inline bool abk_pdl_enabled() {
     }
     return on != 0;
 }
+// cluster_x > 1: the grid's CTAs come as clusters of that many along x (grid.x must be a multiple of it).
+template <typename... KArgs, typename... Args>
+static inline void abk_launch_clusters(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                       int cluster_x, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x, attr[n].val.clusterDim.y = 1, attr[n].val.clusterDim.z = 1;
+        n++;
+    }
+    if (abk_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    cfg.attrs = attr, cfg.numAttrs = n;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);  // the error, if any, is read by ABK_LAUNCH_RESULT
+}
 template <typename... KArgs, typename... Args>
 static inline void abk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               Args &&...args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr, cfg.numAttrs = abk_pdl_enabled() ? 1 : 0;
-    cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);  // the error, if any, is read by ABK_LAUNCH_RESULT
+    abk_launch_clusters(kernel, grid, block, smem, stream, 1, std::forward<Args>(args)...);
 }
 #endif
 

@@ -35,6 +35,12 @@ extern "C" int abk_embed(const int *tokens, const void *table, int table_dtype, 
 // x += y (when y is given); out = w * (x / sqrt(mean(x^2) + eps))      (src/model.c:238-244, 164-169)
 // With `rows`, output row r is made from row rows[r] of x (+ y) and x is left as it is: the
 // final norm of the rows whose logits are wanted.
+__device__ __forceinline__ void store4(float *p, float a, float b, float c, float d) { *(float4 *)p = make_float4(a, b, c, d); }
+__device__ __forceinline__ void store4(__nv_bfloat16 *p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *(uint2 *)p = make_uint2(*(uint32_t *)&lo, *(uint32_t *)&hi);
+}
+
 template <typename TO>
 __global__ void add_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ y, const float *__restrict__ w,
                                    TO *__restrict__ out, const int *__restrict__ rows, int d, float eps) {
@@ -62,11 +68,69 @@ __global__ void add_rmsnorm_kernel(float *__restrict__ x, const float *__restric
     }
 }
 
+// The same with a row in registers (d a multiple of 4 up to 1024 * V, V float4 a thread): the weights come
+// in before pdl_wait(), x and y are read once, and every access is 16 bytes wide.
+template <typename TO, int V>
+__global__ void __launch_bounds__(256) add_rmsnorm_row_kernel(float *__restrict__ x, const float *__restrict__ y,
+                                                              const float *__restrict__ w, TO *__restrict__ out,
+                                                              const int *__restrict__ rows, int d, float eps) {
+    __shared__ float scratch[33];
+    float4 wv[V], v[V];
+#pragma unroll
+    for (int i = 0; i < V; i++) {
+        int j = 4 * (threadIdx.x + 256 * i);
+        wv[i] = j < d ? *(const float4 *)(w + j) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    pdl_wait();
+    const int r = blockIdx.x;
+    const long long src = rows ? rows[r] : r;
+    float *xr = x + src * d;
+    const float *yr = y ? y + src * d : nullptr;
+    const bool update = yr && !rows;
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < V; i++) {
+        int j = 4 * (threadIdx.x + 256 * i);
+        v[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (j < d) {
+            v[i] = *(const float4 *)(xr + j);
+            if (yr) {
+                float4 t = *(const float4 *)(yr + j);
+                v[i].x += t.x, v[i].y += t.y, v[i].z += t.z, v[i].w += t.w;
+            }
+            if (update) *(float4 *)(xr + j) = v[i];
+        }
+        ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    TO *o = out + (long long)r * d;
+#pragma unroll
+    for (int i = 0; i < V; i++) {
+        int j = 4 * (threadIdx.x + 256 * i);
+        if (j < d) store4(o + j, wv[i].x * (v[i].x * scale), wv[i].y * (v[i].y * scale), wv[i].z * (v[i].z * scale),
+                          wv[i].w * (v[i].w * scale));
+    }
+}
+
 extern "C" int abk_add_rmsnorm(float *x, const float *y, const float *w, void *out, int out_dtype, const int *rows,
                                int n_rows, int d, float eps, void *stream) {
     if (n_rows <= 0) return 0;
     int threads = d >= 2048 ? 512 : d >= 512 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
+    const bool aligned = !(((uintptr_t)x | (uintptr_t)y | (uintptr_t)w | (uintptr_t)out) & 15);
+    if (d % 4 == 0 && d <= 4096 && aligned) {
+#define ROW_LAUNCH(TO, V) \
+    abk_launch(add_rmsnorm_row_kernel<TO, V>, dim3(n_rows), dim3(256), 0, s, x, y, w, (TO *)out, rows, d, eps)
+#define ROW_BY_D(TO)                       \
+    if (d <= 1024) ROW_LAUNCH(TO, 1);      \
+    else if (d <= 2048) ROW_LAUNCH(TO, 2); \
+    else ROW_LAUNCH(TO, 4);
+        if (out_dtype == ABK_BF16) { ROW_BY_D(__nv_bfloat16) } else { ROW_BY_D(float) }
+#undef ROW_BY_D
+#undef ROW_LAUNCH
+        return ABK_LAUNCH_RESULT();
+    }
     if (out_dtype == ABK_BF16)
         abk_launch(add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, s, x, y, w, (__nv_bfloat16 *)out, rows, d, eps);
     else
@@ -219,7 +283,8 @@ template <int N> struct __align__(2 * N) Bf16Pack { __nv_bfloat16 v[N]; };
 template <int EPH> __global__ void __launch_bounds__(FAST_WARPS * 32) qkv_prep_fast_kernel(QkvPrep p) {
     constexpr int HD = 64 * EPH, HALF = 32 * EPH;
     typedef Bf16Pack<EPH> Pack;
-    pdl_wait();
+    // Everything but the row itself (the step's index arrays, the page table, the norm's weights, the
+    // angles) was written by kernels further back than the one just before this, and is read before pdl_wait().
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * FAST_WARPS + warp;
     const int total_heads = p.n_heads + 2 * p.n_kv_heads;
@@ -230,6 +295,25 @@ template <int EPH> __global__ void __launch_bounds__(FAST_WARPS * 32) qkv_prep_f
     __nv_bfloat16 *row = (__nv_bfloat16 *)p.qkv + ((long long)t * total_heads + head) * HD + lane * EPH;
     const bool is_q = head < p.n_heads, is_k = !is_q && head < p.n_heads + p.n_kv_heads;
     const int kv_head = is_q ? 0 : is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
+    const float *w = is_q ? p.q_norm : p.k_norm;
+    float w_lo[EPH], w_hi[EPH], cs[EPH], sn[EPH];
+    if ((is_q || is_k) && w) {
+#pragma unroll
+        for (int e = 0; e < EPH; e++) w_lo[e] = w[lane * EPH + e], w_hi[e] = w[HALF + lane * EPH + e];
+    }
+    if ((is_q || is_k) && p.cos) {
+        const float *c = p.cos + (long long)pos * HALF + lane * EPH, *sp = p.sin + (long long)pos * HALF + lane * EPH;
+#pragma unroll
+        for (int e = 0; e < EPH; e++) cs[e] = c[e], sn[e] = sp[e];
+    }
+    __nv_bfloat16 *dst = nullptr;  // where the key or value goes in the cache, if it is kept
+    if (!is_q && p.k_pool &&
+        !(p.cache.ring_pages > 0 && pos + p.cache.ring_pages * p.cache.tokens_per_page <= p.seq_len_after[seq] - 1)) {
+        const int page = cache_page(p.cache, p.seq_slot[seq], pos);
+        dst = (__nv_bfloat16 *)(is_k ? p.k_pool : p.v_pool) + cache_offset(p.cache, page, kv_head, p.n_kv_heads, pos, HD) +
+              lane * EPH;
+    }
+    pdl_wait();
     Pack lo = *(const Pack *)row, hi = *(const Pack *)(row + HALF);
     if (is_q || is_k) {
         float a[EPH], b[EPH], ss = 0.0f;
@@ -238,37 +322,28 @@ template <int EPH> __global__ void __launch_bounds__(FAST_WARPS * 32) qkv_prep_f
             a[e] = __bfloat162float(lo.v[e]), b[e] = __bfloat162float(hi.v[e]);
             ss += a[e] * a[e] + b[e] * b[e];
         }
-        const float *w = is_q ? p.q_norm : p.k_norm;
         if (w) {
             ss = warp_sum(ss);
             const float scale = 1.0f / sqrtf(ss / (float)HD + p.eps);
 #pragma unroll
             for (int e = 0; e < EPH; e++) {
-                a[e] = w[lane * EPH + e] * (a[e] * scale);
-                b[e] = w[HALF + lane * EPH + e] * (b[e] * scale);
+                a[e] = w_lo[e] * (a[e] * scale);
+                b[e] = w_hi[e] * (b[e] * scale);
             }
         }
         if (p.cos) {
-            const float *c = p.cos + (long long)pos * HALF + lane * EPH, *s = p.sin + (long long)pos * HALF + lane * EPH;
 #pragma unroll
             for (int e = 0; e < EPH; e++) {
                 float x = a[e], y = b[e];
-                a[e] = x * c[e] - y * s[e];
-                b[e] = y * c[e] + x * s[e];
+                a[e] = x * cs[e] - y * sn[e];
+                b[e] = y * cs[e] + x * sn[e];
             }
         }
 #pragma unroll
         for (int e = 0; e < EPH; e++) lo.v[e] = __float2bfloat16_rn(a[e]), hi.v[e] = __float2bfloat16_rn(b[e]);
         *(Pack *)row = lo, *(Pack *)(row + HALF) = hi;
     }
-    if (is_q || !p.k_pool) return;
-    if (p.cache.ring_pages > 0 &&
-        pos + p.cache.ring_pages * p.cache.tokens_per_page <= p.seq_len_after[seq] - 1)
-        return;
-    const int page = cache_page(p.cache, p.seq_slot[seq], pos);
-    __nv_bfloat16 *dst = (__nv_bfloat16 *)(is_k ? p.k_pool : p.v_pool) +
-                         cache_offset(p.cache, page, kv_head, p.n_kv_heads, pos, HD) + lane * EPH;
-    *(Pack *)dst = lo, *(Pack *)(dst + HALF) = hi;
+    if (dst) *(Pack *)dst = lo, *(Pack *)(dst + HALF) = hi;
 }
 
 extern "C" int abk_qkv_prep(void *qkv, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int q_only,

@@ -8,9 +8,15 @@
 // the 32 columns sit in which slot of the product. No shared-memory staging, no barrier in the
 // loop, no scratch memory: the eight partial tiles are added in warp order at the end, so the
 // result does not depend on timing. float32 accumulation.
+//
+// A matrix with few rows and a long K (the projections back to the model's width) gives few CTAs, each
+// with several turns of loads one after the other. Its CTAs come as clusters of up to 8 that split K
+// between them, one turn each; the first CTA of a cluster adds the others' sums, in their order,
+// reading them through distributed shared memory.
 // Formula: src/model.c:299, 302, 307, 309.
 #define ABK_DEFINE_ERROR
 #include "common.cuh"
+#include "tc_common.cuh"
 
 #define ROWS_WARPS 8
 #define ROWS_THREADS (32 * ROWS_WARPS)
@@ -42,32 +48,50 @@ __device__ __forceinline__ uint4 load16(const __nv_bfloat16 *p, bool ok) {
 // GATED: w holds N gate rows and then N up rows (src/model.c:98); a CTA owns 8 outputs, takes their gate
 // rows as the lower and their up rows as the upper half of the product, and stores silu(gate) * up
 // (src/model.c:274-282) instead of the two sums: the feed-forward's first product and its activation in one.
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 template <int NT, int TILE, bool GATED, typename TO>
 __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bfloat16 *__restrict__ x,
                                                                  const __nv_bfloat16 *__restrict__ w, TO *__restrict__ out,
                                                                  int M, int N, int K, long long ldx, long long ldw,
                                                                  long long ldo) {
     __shared__ float part[ROWS_WARPS][16][8 * NT + 1];
-    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
-    const int n0 = blockIdx.x * TILE;
+    const int ranks = (int)tc::cluster_size(), rank = (int)tc::cluster_rank();  // the cluster splits K
+    const int n0 = (blockIdx.x / ranks) * TILE;
     const bool row_lo = n0 + r < N, row_hi = GATED ? row_lo : TILE == 16 && n0 + r + 8 < N;
     const __nv_bfloat16 *w_lo = w + (long long)(n0 + r) * ldw + 8 * c, *w_hi = w_lo + (GATED ? (long long)N : 8) * ldw;
     const __nv_bfloat16 *x0 = x + (long long)r * ldx + 8 * c;  // token r of tile t is 8 t rows further
     float acc[NT][4];
 #pragma unroll
     for (int t = 0; t < NT; t++) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
-    const int blocks = K / 32;
+    const int blocks = (rank + 1) * (K / 32 / ranks), first = rank * (K / 32 / ranks) + warp;  // this CTA's part of K
     // several blocks of 32 columns a turn, so that eight 16-byte loads of weights are in flight per lane
     constexpr int TURN = NT <= 2 ? 4 : 2;
-    for (int kb = warp; kb < blocks; kb += TURN * ROWS_WARPS) {
-        uint4 a_lo[TURN], a_hi[TURN], b[TURN][NT];
+    uint4 a_lo[TURN], a_hi[TURN], b[TURN][NT];
+    auto load_weights = [&](int kb) {
 #pragma unroll
         for (int u = 0; u < TURN; u++) {
             int k = (kb + u * ROWS_WARPS) * 32;
             bool in = kb + u * ROWS_WARPS < blocks;
             a_lo[u] = load16(w_lo + k, in && row_lo);
             a_hi[u] = TILE == 16 || GATED ? load16(w_hi + k, in && row_hi) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    // The weights are nobody's output: the first turn's are fetched, and the later turns' called into the L2,
+    // before pdl_wait(), while the kernel that writes x is still running.
+    load_weights(first);
+    for (int kb = first + TURN * ROWS_WARPS; kb < blocks; kb += ROWS_WARPS) {
+        if (row_lo) prefetch_l2(w_lo + kb * 32);
+        if ((TILE == 16 || GATED) && row_hi) prefetch_l2(w_hi + kb * 32);
+    }
+    pdl_wait();
+    for (int kb = first; kb < blocks; kb += TURN * ROWS_WARPS) {
+        if (kb != first) load_weights(kb);
+#pragma unroll
+        for (int u = 0; u < TURN; u++) {
+            int k = (kb + u * ROWS_WARPS) * 32;
+            bool in = kb + u * ROWS_WARPS < blocks;
 #pragma unroll
             for (int t = 0; t < NT; t++) b[u][t] = load16(x0 + (long long)(8 * t) * ldx + k, in && 8 * t + r < M);
         }
@@ -87,6 +111,34 @@ __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bflo
         part[warp][r + 8][8 * t + 2 * c] = acc[t][2], part[warp][r + 8][8 * t + 2 * c + 1] = acc[t][3];
     }
     __syncthreads();
+    if (ranks > 1) {
+        // the warps' sums become the CTA's (kept in the first warp's tile), the first CTA adds the other CTAs'
+        for (int i = threadIdx.x; i < 16 * 8 * NT; i += ROWS_THREADS) {
+            int row = i / (8 * NT), token = i % (8 * NT);
+            float sum = 0.0f;
+#pragma unroll
+            for (int wv = 0; wv < ROWS_WARPS; wv++) sum += part[wv][row][token];
+            part[0][row][token] = sum;  // each element is read and written by this thread alone
+        }
+        tc::cluster_sync();
+        if (rank == 0) {
+            for (int i = threadIdx.x; i < TILE * 8 * NT; i += ROWS_THREADS) {
+                int token = i / TILE, row = i % TILE;
+                if (token < M && n0 + row < N) {
+                    float sum = part[0][row][token];
+                    const uint32_t at = (uint32_t)__cvta_generic_to_shared(&part[0][row][token]);
+                    for (int c = 1; c < ranks; c++) {
+                        float v;
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(tc::peer_smem(at, c)));
+                        sum += v;
+                    }
+                    out[(long long)token * ldo + n0 + row] = from_float<TO>(sum);
+                }
+            }
+        }
+        tc::cluster_sync();  // nobody leaves while its sums may still be read
+        return;
+    }
     for (int i = threadIdx.x; i < TILE * 8 * NT; i += ROWS_THREADS) {
         int token = i / TILE, row = i % TILE;  // consecutive threads write consecutive features of a token
         if (token < M && n0 + row < N) {
@@ -115,11 +167,19 @@ extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dt
     if (K <= 0 || K % 32 || ldx % 8 || ldw % 8) ABK_REFUSE("gemm_rows: K = %d must be a multiple of 32 and the pitches of 8", K);
     if (((uintptr_t)x | (uintptr_t)w) & 15) ABK_REFUSE("gemm_rows: operands must be 16-byte aligned");
     const bool narrow = (N + 15) / 16 < 2 * 148;  // too few tiles of 16 for two CTAs on every SM
-    dim3 grid(narrow ? (N + 7) / 8 : (N + 15) / 16);
+    const int tiles = narrow ? (N + 7) / 8 : (N + 15) / 16;
+    // a long K over few tiles: clusters that split K, one turn of loads to a CTA, while the grid stays small
+    const int turn = 32 * ROWS_WARPS * (M <= 16 ? 4 : 2);
+    int ranks = narrow ? K / turn : 1;
+    if (ranks > 8) ranks = 8;
+    while (ranks > 1 && ((K / 32) % ranks || (long long)tiles * ranks > 8 * 148)) ranks--;
+    if (ranks < 1) ranks = 1;
+    dim3 grid(tiles * ranks);
     cudaStream_t s = (cudaStream_t)stream;
     const __nv_bfloat16 *xb = (const __nv_bfloat16 *)x, *wb = (const __nv_bfloat16 *)w;
-#define ROWS_LAUNCH(NT, TILE, TO) \
-    abk_launch(gemm_rows_kernel<NT, TILE, false, TO>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (TO *)out, M, N, K, ldx, ldw, ldo)
+#define ROWS_LAUNCH(NT, TILE, TO)                                                                                     \
+    abk_launch_clusters(gemm_rows_kernel<NT, TILE, false, TO>, grid, dim3(ROWS_THREADS), 0, s, ranks, xb, wb, (TO *)out, M, \
+                        N, K, ldx, ldw, ldo)
 #define ROWS_BY_M(TO)                                                                     \
     if (M <= 8) { if (narrow) ROWS_LAUNCH(1, 8, TO); else ROWS_LAUNCH(1, 16, TO); }       \
     else if (M <= 16) { if (narrow) ROWS_LAUNCH(2, 8, TO); else ROWS_LAUNCH(2, 16, TO); } \

@@ -27,6 +27,14 @@ MODULES = ("elementwise", "gemm_simt", "gemm_tc", "attention_generic", "attentio
            "sampling", "attention_decode_static", "attention_decode_ring", "attention_tc")
 
 
+# ABACUS_TRACE=1 builds every library with the launch-timeline records of csrc/common.cuh compiled in
+TRACE = os.environ.get("ABACUS_TRACE", "0") not in ("", "0")
+
+
+def _module_flags(module):
+    return [f"-DABK_TRACE={MODULES.index(module)}"] if TRACE else []
+
+
 class KernelBuildError(RuntimeError):
     pass
 
@@ -63,7 +71,7 @@ def _build_dir():
 
 def _fingerprint(module):
     h = hashlib.sha256()
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + _module_flags(module)).encode())
     with open(os.path.join(CSRC, module + ".cu")) as f:
         included = {line.split('"')[1] for line in f if line.startswith("#include \"") and line.count('"') >= 2}
     for name in sorted(os.listdir(CSRC)):
@@ -98,7 +106,7 @@ def compile_module(module, verbose=True, extra_flags=()):
                                "(set ABACUS_NVCC or put nvcc on PATH)")
     out = library_path(module)
     tmp = f"{out}.{os.getpid()}.tmp"
-    cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *extra_flags, "-I", CSRC, "-o", tmp, src]
+    cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *_module_flags(module), *extra_flags, "-I", CSRC, "-o", tmp, src]
     if verbose:
         print(f"abacus_b200: compiling {module}.cu for sm_100a ...", file=sys.stderr, flush=True)
     start = time.time()
