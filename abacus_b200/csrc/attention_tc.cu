@@ -9,11 +9,16 @@
 //              tensor memory) and O += P V (128 x 128, P from shared memory, V as an MN-major
 //              operand straight from the page), S of the next page before O of this one, so that
 //              the softmax of page j+1 runs under the second product of page j;
-//   warps 2-5  one thread per query row: reads its row of S from tensor memory (tcgen05.ld),
-//              scales, masks (only pages that cross the diagonal), keeps the running maximum and
-//              sum in float32, writes P as bfloat16 into shared memory in the swizzled layout the
-//              tensor core reads, and, when the maximum has outgrown its reference by 2^8, rescales its
-//              row of O in tensor memory (tcgen05.ld / tcgen05.st) between two second products.
+//   warps 2-9  two threads per query row, 32 of the page's 64 keys each (a warp reaches only its own
+//              quarter of the lanes of tensor memory, so warps w and w + 4 share 32 rows): each reads
+//              its half row of S (tcgen05.ld), masks (only pages that cross the diagonal), and swaps
+//              its maximum with its partner through shared memory; both then hold the row's maximum,
+//              keep the same reference, and each writes its half of P as bfloat16 into shared memory
+//              in the swizzled layout the tensor core reads, keeps its half of the row's sum, and, when
+//              the maximum has outgrown the reference by 2^8, rescales its half of the row of O in
+//              tensor memory (tcgen05.ld / tcgen05.st) between two second products. A step of a
+//              (sequence, head) is bound by this chain, not by the tensor cores: halving the row
+//              halves every dependent run of instructions in it.
 // Tensor memory: 2 x 64 columns of scores + 128 columns of output = 256 of 512. Every wait on an
 // mbarrier is bounded; a wait that runs out sets status word 3 and the CTA winds down.
 // Formula: src/model.c:197-211; softmax in float32, probabilities rounded to bfloat16 for P V.
@@ -26,7 +31,7 @@
 #define TK 64         // keys per step: one page
 #define HD 128
 #define KV_STAGES 2   // with the query tile and one P tile: 112 KB, two CTAs to an SM
-#define FA_THREADS 192
+#define FA_THREADS 320
 #define Q_BYTES (TQ * HD * 2)       // two boxes of [128 rows, 64 columns]
 #define KV_BYTES (TK * HD * 2)      // two boxes of [64 rows, 64 columns]
 #define P_BYTES (TQ * TK * 2)       // one box of [128 rows, 64 columns]
@@ -73,37 +78,60 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// The two warps of a quarter (64 threads) meet; the ids are literal so that the CTA asks for five barriers, not sixteen.
+__device__ __forceinline__ void pair_sync(int quarter) {
+    switch (quarter) {
+    case 0: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
+    case 1: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+    case 2: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+    default: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+    }
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__global__ void __launch_bounds__(FA_THREADS) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
+__global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                                                                      const __grid_constant__ CUtensorMap k_map,
                                                                      const __grid_constant__ CUtensorMap v_map, AttnTc p) {
     extern __shared__ __align__(1024) uint8_t smem[];  // the kernel has no static shared memory: this starts aligned
     uint8_t *q_s = smem, *k_s = q_s + Q_BYTES, *v_s = k_s + KV_STAGES * KV_BYTES, *p_s = v_s + KV_STAGES * KV_BYTES;
     uint64_t *bars = (uint64_t *)(p_s + P_BYTES);
-    uint64_t *q_full = bars, *kv_full = bars + 1, *kv_empty = kv_full + KV_STAGES, *s_full = kv_empty + KV_STAGES,
-             *p_full = s_full + 2, *o_step = p_full + 2;  // o_step: the second product of a page is done
+    uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = k_full + KV_STAGES, *v_full = k_empty + KV_STAGES,
+             *v_empty = v_full + KV_STAGES, *s_full = v_empty + KV_STAGES, *p_full = s_full + 2,
+             *o_step = p_full + 2;  // o_step: the second product of a page is done
     uint32_t *tmem_holder = (uint32_t *)(o_step + 1);
     volatile int *failed = (volatile int *)(tmem_holder + 1);
+    // [2 halves][128 rows]: the halves' maxima, rounded up to bfloat16 (any common bound of the row's scores
+    // serves as the reference; the few bytes more that float32 would take are the difference between one and two
+    // CTAs on an SM)
+    __nv_bfloat16 *swap = (__nv_bfloat16 *)(tmem_holder + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (*(volatile int *)(p.status + 3)) return;  // an earlier CTA gave up on a wait: do not queue up behind it
+#ifdef ABK_TRACE
+    const unsigned long long trace_begin = abk_trace_ns();
+#endif
+    // Before pdl_wait(): what kernels further back than the one just before this wrote (the step's index arrays,
+    // the page table), and the CTA's own set-up. The loads that do not depend on one another go out together.
     const int seq = p.tiles[2 * blockIdx.x], row0 = p.tiles[2 * blockIdx.x + 1], h = blockIdx.y;
-    const int kvh = h / (p.n_heads / p.n_kv_heads);
-    const int start = p.seq_start[seq], pos0 = p.seq_pos0[seq], n_new = p.seq_len_after[seq] - pos0;
-    const int last_row = min(row0 + TQ - 1, n_new - 1);
-    const int n_steps = (pos0 + last_row) / TK + 1;  // pages of keys the tile's last row sees
-
+    // an earlier CTA gave up on a wait: do not queue up behind it (one thread looks, so that all decide alike)
     if (threadIdx.x == 0) {
+        *(volatile int *)swap = *(volatile int *)(p.status + 3);
         *failed = 0;
         tc::mbar_init(q_full, 1);
-        for (int s = 0; s < KV_STAGES; s++) tc::mbar_init(&kv_full[s], 1), tc::mbar_init(&kv_empty[s], 1);
-        for (int b = 0; b < 2; b++) tc::mbar_init(&s_full[b], 1), tc::mbar_init(&p_full[b], 128);
+        for (int s = 0; s < KV_STAGES; s++)
+            tc::mbar_init(&k_full[s], 1), tc::mbar_init(&k_empty[s], 1), tc::mbar_init(&v_full[s], 1), tc::mbar_init(&v_empty[s], 1);
+        for (int b = 0; b < 2; b++) tc::mbar_init(&s_full[b], 1), tc::mbar_init(&p_full[b], 256);
         tc::mbar_init(o_step, 1);
         tc::mbar_init_fence();
         tc::tma_prefetch_map(&q_map), tc::tma_prefetch_map(&k_map), tc::tma_prefetch_map(&v_map);
     }
+    const int kvh = h / (p.n_heads / p.n_kv_heads);
+    const int start = p.seq_start[seq], pos0 = p.seq_pos0[seq], n_new = p.seq_len_after[seq] - pos0;
+    const int slot = p.seq_slot[seq];
+    const int last_row = min(row0 + TQ - 1, n_new - 1);
+    const int n_steps = (pos0 + last_row) / TK + 1;  // pages of keys the tile's last row sees
+    __syncthreads();
+    if (*(volatile int *)swap) return;  // swap is first written for its own purpose after the next barrier
     if (warp == 1) tc::tmem_alloc(tmem_holder, 256);
     tc::fence_before_sync();
     __syncthreads();
@@ -111,28 +139,54 @@ __global__ void __launch_bounds__(FA_THREADS) attn_prefill_tc_kernel(const __gri
     const uint32_t tmem = *tmem_holder, tmem_o = tmem + 128;
 
     if (warp == 0) {
-        if (lane == 0) {
-            tc::mbar_expect_tx(q_full, Q_BYTES);
-            tc::tma_load_2d(q_s, &q_map, h * HD, start + row0, q_full);
-            tc::tma_load_2d(q_s + BOX_Q, &q_map, h * HD + 64, start + row0, q_full);
-            const int slot = p.seq_slot[seq];
-            int issued = 0;
-            for (int j = 0; j < n_steps; j++, issued++) {
-                int s = j % KV_STAGES;
-                if (!tc::mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1)) {
-                    atomicOr(p.status + 3, 2);
-                    *failed = 1;
-                    break;
+        // Keys and values have rings of their own: a stage of keys is free once the first product of its
+        // page is done, a whole step before the stage of values is, so the next keys are under way that
+        // much earlier and the first product of a step does not wait for its load. Every lane looks up the
+        // pool row of one of the next 32 pages, so that the table's latency is paid once for all of them.
+        int k_issued = 0, v_issued = 0;
+        bool go = true;
+        for (int base = 0; base < n_steps && go; base += 32) {
+            const int y_lane = base + lane < n_steps ? (cache_page(p.cache, slot, (base + lane) * TK) * p.n_kv_heads + kvh) * TK : 0;
+            if (base == 0) {
+                pdl_wait();  // q, and the keys and values of this step's tokens, come from the kernel just before
+                if (lane == 0) {
+                    tc::mbar_expect_tx(q_full, Q_BYTES);
+                    tc::tma_load_2d(q_s, &q_map, h * HD, start + row0, q_full);
+                    tc::tma_load_2d(q_s + BOX_Q, &q_map, h * HD + 64, start + row0, q_full);
                 }
-                int y = (cache_page(p.cache, slot, j * TK) * p.n_kv_heads + kvh) * TK;
-                tc::mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
-                tc::tma_load_2d(k_s + s * KV_BYTES, &k_map, 0, y, &kv_full[s]);
-                tc::tma_load_2d(k_s + s * KV_BYTES + BOX_KV, &k_map, 64, y, &kv_full[s]);
-                tc::tma_load_2d(v_s + s * KV_BYTES, &v_map, 0, y, &kv_full[s]);
-                tc::tma_load_2d(v_s + s * KV_BYTES + BOX_KV, &v_map, 64, y, &kv_full[s]);
             }
-            if (*failed)
-                for (int i = max(0, issued - KV_STAGES); i < issued; i++) tc::mbar_wait(&kv_full[i % KV_STAGES], (i / KV_STAGES) & 1);
+            const int n = min(32, n_steps - base);
+            for (int i = 0; i < n && go; i++) {
+                const int j = base + i, s = j % KV_STAGES;
+                const uint32_t parity = ((j / KV_STAGES) & 1) ^ 1;
+                const int y = __shfl_sync(0xffffffffu, y_lane, i);
+                int bad = 0;
+                if (lane == 0) {
+                    if (!tc::mbar_wait(&k_empty[s], parity)) {
+                        bad = 1;
+                    } else {
+                        tc::mbar_expect_tx(&k_full[s], KV_BYTES);
+                        tc::tma_load_2d(k_s + s * KV_BYTES, &k_map, 0, y, &k_full[s]);
+                        tc::tma_load_2d(k_s + s * KV_BYTES + BOX_KV, &k_map, 64, y, &k_full[s]);
+                        k_issued++;
+                        if (!tc::mbar_wait(&v_empty[s], parity)) {
+                            bad = 1;
+                        } else {
+                            tc::mbar_expect_tx(&v_full[s], KV_BYTES);
+                            tc::tma_load_2d(v_s + s * KV_BYTES, &v_map, 0, y, &v_full[s]);
+                            tc::tma_load_2d(v_s + s * KV_BYTES + BOX_KV, &v_map, 64, y, &v_full[s]);
+                            v_issued++;
+                        }
+                    }
+                }
+                if (__shfl_sync(0xffffffffu, bad, 0)) go = false;
+            }
+        }
+        if (!go && lane == 0) {  // let the copies in flight land before the CTA's memory goes away
+            atomicOr(p.status + 3, 2);
+            *failed = 1;
+            for (int i = max(0, k_issued - KV_STAGES); i < k_issued; i++) tc::mbar_wait(&k_full[i % KV_STAGES], (i / KV_STAGES) & 1);
+            for (int i = max(0, v_issued - KV_STAGES); i < v_issued; i++) tc::mbar_wait(&v_full[i % KV_STAGES], (i / KV_STAGES) & 1);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -144,7 +198,7 @@ __global__ void __launch_bounds__(FA_THREADS) attn_prefill_tc_kernel(const __gri
             for (int j = 0; j <= n_steps && ok; j++) {
                 if (j < n_steps) {
                     const int s = j % KV_STAGES, b = j & 1;
-                    ok = ok && tc::mbar_wait(&kv_full[s], (j / KV_STAGES) & 1);
+                    ok = ok && tc::mbar_wait(&k_full[s], (j / KV_STAGES) & 1);
                     if (!ok) atomicOr(p.status + 3, 8);
                     // the score buffer is free once the softmax of step j-2 has delivered its P
                     if (ok && j >= 2) {
@@ -158,10 +212,12 @@ __global__ void __launch_bounds__(FA_THREADS) attn_prefill_tc_kernel(const __gri
                     for (int k16 = 0; k16 < HD / 16; k16++)
                         tc::mma_ss(tmem + b * TK, k_major_desc(qa, BOX_Q, k16), k_major_desc(kb, BOX_KV, k16), idesc_s, k16 > 0);
                     tc::mma_commit(&s_full[b]);
+                    tc::mma_commit(&k_empty[s]);  // the page's keys may be replaced
                 }
                 if (j >= 1) {
                     const int i = j - 1, s = i % KV_STAGES, b = i & 1;
                     ok = tc::mbar_wait(&p_full[b], (i >> 1) & 1);  // P(i) is in shared memory, O is rescaled
+                    ok = ok && tc::mbar_wait(&v_full[s], (i / KV_STAGES) & 1);
                     if (!ok) {
                         atomicOr(p.status + 3, 32);
                         break;
@@ -172,80 +228,100 @@ __global__ void __launch_bounds__(FA_THREADS) attn_prefill_tc_kernel(const __gri
                     for (int k16 = 0; k16 < TK / 16; k16++)
                         tc::mma_ss(tmem_o, tc::smem_desc_k_sw128(pa + k16 * 32), smem_desc_mn_sw128(vb + k16 * 2048, BOX_KV),
                                    idesc_o, i > 0 || k16 > 0);
-                    tc::mma_commit(&kv_empty[s]);  // the page's stage may be refilled
+                    tc::mma_commit(&v_empty[s]);  // the page's values may be replaced
                     tc::mma_commit(o_step);        // and the softmax warps may touch O again
                 }
             }
             if (!ok) *failed = 1;
         }
     } else {
+        pdl_wait();  // before anything is written to global memory
         const int quarter = warp & 3, r = quarter * 32 + lane;   // this thread's query row within the tile
+        const int half = (warp - 2) >> 2, col0 = half * (TK / 2);  // and its 32 of a page's 64 keys
         const int qpos = pos0 + row0 + r;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        float m = -INFINITY, l = 0.0f;
+        float m = -INFINITY, l = 0.0f;  // l: the sum over this thread's keys only
         bool ok = true;
-        for (int j = 0; j < n_steps && ok; j++) {
+        const float GONE = __int_as_float(0x7fc00000);  // what a warp that has given up leaves for its partner
+        for (int j = 0; j < n_steps; j++) {
             const int b = j & 1;
-            if (!tc::mbar_wait(&s_full[b], (j >> 1) & 1)) {
-                atomicOr(p.status + 3, 64);
+            // The two warps of a quarter meet at a barrier in every step, so they must leave the loop in the
+            // same step: a warp that ran out of time says so through the value it swaps, and both go.
+            bool fine = ok && tc::mbar_wait(&s_full[b], (j >> 1) & 1);
+            fine = __all_sync(0xffffffffu, fine);
+            if (ok && !fine) atomicOr(p.status + 3, 64);
+            float s[TK / 2];
+            float mx = -INFINITY;  // of the raw scores; the scale (positive) is applied to the maximum
+            if (fine) {
+                tc::fence_after_sync();
+#pragma unroll
+                for (int c0 = 0; c0 < TK / 2; c0 += 16) tc::tmem_ld16(tmem + lane_base + b * TK + col0 + c0, (uint32_t *)(s + c0));
+                tc::tmem_ld_wait();
+                const bool edge = j * TK + TK - 1 > pos0 + row0;  // some key of this page lies after some row of the tile
+                if (edge) {
+#pragma unroll
+                    for (int c = 0; c < TK / 2; c++)
+                        if (j * TK + col0 + c > qpos) s[c] = -INFINITY;
+                }
+                // two runs of maxima instead of one of 32 dependent instructions
+                float mx2 = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < TK / 2; c += 2) mx = fmaxf(mx, s[c]), mx2 = fmaxf(mx2, s[c + 1]);
+                mx = fmaxf(mx, mx2);
+            }
+            const __nv_bfloat16 mine_up = __float2bfloat16_ru(fine ? mx : GONE);
+            pair_sync(quarter);  // the partner has read what the step before left here
+            swap[half * TQ + r] = mine_up;
+            pair_sync(quarter);
+            const float theirs = __bfloat162float(swap[(half ^ 1) * TQ + r]);
+            if (__any_sync(0xffffffffu, !fine || theirs != theirs)) {
                 ok = false;
                 break;
             }
-            tc::fence_after_sync();
-            float s[TK];
-#pragma unroll
-            for (int c0 = 0; c0 < TK; c0 += 16) tc::tmem_ld16(tmem + lane_base + b * TK + c0, (uint32_t *)(s + c0));
-            tc::tmem_ld_wait();
-            const bool edge = j * TK + TK - 1 > pos0 + row0;  // some key of this page lies after some row of the tile
-            float mx = -INFINITY;  // of the raw scores; the scale (positive) is applied to the maximum
-            if (edge) {
-#pragma unroll
-                for (int c = 0; c < TK; c++)
-                    if (j * TK + c > qpos) s[c] = -INFINITY;
-            }
-#pragma unroll
-            for (int c = 0; c < TK; c++) mx = fmaxf(mx, s[c]);
+            mx = fmaxf(__bfloat162float(mine_up), theirs);
             mx *= p.scale_log2;
             // `m` is the reference the row's exponentials, its sum and its O are scaled by. It follows the
             // true maximum only when that has outgrown it by 2^8 (the probabilities stay below 256, well
             // inside bfloat16 and float32), so that O is rescaled on a few early steps only; the final
-            // O / l does not depend on the reference.
+            // O / l does not depend on the reference. Both warps of a quarter see the same maxima and
+            // the same references, so they decide alike.
             const float cand = fmaxf(m, mx);
             const bool move = __any_sync(0xffffffffu, cand > m + 8.0f);  // the first step: m is -inf
             const float m_new = move ? cand : m;
             const float ref = m_new == -INFINITY ? 0.0f : m_new;
             const float corr = exp2f(m - ref);
-            float sum = 0.0f;
-            uint32_t packed[TK / 2];
+            float sum0 = 0.0f, sum1 = 0.0f;
+            uint32_t packed[TK / 4];
 #pragma unroll
-            for (int c = 0; c < TK; c += 2) {
+            for (int c = 0; c < TK / 2; c += 2) {
                 float p0 = ex2(fmaf(s[c], p.scale_log2, -ref)), p1 = ex2(fmaf(s[c + 1], p.scale_log2, -ref));
-                sum += p0 + p1;
+                sum0 += p0, sum1 += p1;
                 __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
                 packed[c / 2] = *(uint32_t *)&t;
             }
-            l = l * corr + sum;
+            l = l * corr + (sum0 + sum1);
             // P's tile and O may be touched only between two second products: wait for the one of step j-1
-            if (j >= 1 && !tc::mbar_wait(o_step, (j - 1) & 1)) {
+            if (j >= 1 && !__all_sync(0xffffffffu, tc::mbar_wait(o_step, (j - 1) & 1))) {
                 atomicOr(p.status + 3, 128);
-                ok = false;
-                break;
+                ok = false;  // the partner hears of it at the next step's barrier (or both are through)
+                continue;
             }
-            // P(j) as a K-major operand: row r, 128 bytes, eight 16-byte chunks swizzled by the row
+            // P(j) as a K-major operand: row r, 128 bytes, eight 16-byte chunks swizzled by the row; this thread's four
             uint8_t *prow = p_s + r * 128;
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++)
-                *(uint4 *)(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+            for (int ch = 0; ch < 4; ch++)
+                *(uint4 *)(prow + (((4 * half + ch) ^ (r & 7)) << 4)) =
+                    make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
             if (j >= 1 && move) {
                 tc::fence_after_sync();
 #pragma unroll 1
-                for (int c0 = 0; c0 < HD; c0 += 16) {
+                for (int c0 = 0; c0 < HD / 2; c0 += 16) {
                     uint32_t v[16];
-                    tc::tmem_ld16(tmem_o + lane_base + c0, v);
+                    tc::tmem_ld16(tmem_o + lane_base + half * (HD / 2) + c0, v);
                     tc::tmem_ld_wait();
 #pragma unroll
                     for (int e = 0; e < 16; e++) v[e] = __float_as_uint(__uint_as_float(v[e]) * corr);
-                    tmem_st16(tmem_o + lane_base + c0, v);
+                    tmem_st16(tmem_o + lane_base + half * (HD / 2) + c0, v);
                 }
                 tmem_st_wait();
             }
@@ -261,20 +337,25 @@ __global__ void __launch_bounds__(FA_THREADS) attn_prefill_tc_kernel(const __gri
         }
         if (!ok) *failed = 1;
         tc::fence_after_sync();
+        // the row's sum is the two halves' (their reference is the same); P's tile is free now and carries them
+        float *sums = (float *)p_s;
+        sums[half * TQ + r] = l;
+        pair_sync(quarter);
+        l += sums[(half ^ 1) * TQ + r];
         // tcgen05.ld is a whole-warp instruction: every lane reads its row, only rows of the sequence are stored
         if (__all_sync(0xffffffffu, ok)) {
             const bool mine = row0 + r < n_new;
             const float inv = 1.0f / l;
-            __nv_bfloat16 *dst = p.out + ((long long)(start + row0 + r) * p.n_heads + h) * HD;
+            __nv_bfloat16 *dst = p.out + ((long long)(start + row0 + r) * p.n_heads + h) * HD + half * (HD / 2);
 #pragma unroll 1
-            for (int c0 = 0; c0 < HD; c0 += 16) {
+            for (int c0 = 0; c0 < HD / 2; c0 += 16) {
                 uint32_t v[16], hpk[8];
-                tc::tmem_ld16(tmem_o + lane_base + c0, v);
+                tc::tmem_ld16(tmem_o + lane_base + half * (HD / 2) + c0, v);
                 tc::tmem_ld_wait();
 #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[2 * e]) * inv, __uint_as_float(v[2 * e + 1]) * inv);
-                    hpk[e] = *(uint32_t *)&t;
+                for (int e2 = 0; e2 < 8; e2++) {
+                    __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[2 * e2]) * inv, __uint_as_float(v[2 * e2 + 1]) * inv);
+                    hpk[e2] = *(uint32_t *)&t;
                 }
                 if (mine) {
                     *(uint4 *)(dst + c0) = make_uint4(hpk[0], hpk[1], hpk[2], hpk[3]);
@@ -290,6 +371,14 @@ __global__ void __launch_bounds__(FA_THREADS) attn_prefill_tc_kernel(const __gri
         tc::fence_after_sync();
         tc::tmem_free(tmem, 256);
     }
+#ifdef ABK_TRACE
+    if (threadIdx.x == 0) {  // every CTA's life: begin, end, its tile and head, its steps and its SM
+        unsigned int i = atomicAdd(&abk_trace_count, 1u), sm;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+        if (i < ABK_TRACE_MAX)
+            abk_trace_records[i] = {trace_begin, abk_trace_ns(), ABK_TRACE, (int)(blockIdx.x + (blockIdx.y << 16)), n_steps, (int)sm};
+    }
+#endif
 }
 
 // qkv: the step's rows [n_rows, row_width] (q columns first); out [n_rows, n_heads * 128].
@@ -316,13 +405,13 @@ extern "C" int abk_attention_prefill_tc(const void *qkv, long long row_width, in
     p.seq_len_after = seq_len_after, p.seq_slot = seq_slot, p.status = status;
     p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = 0;
     p.cache.tokens_per_page = tokens_per_page;
-    const int smem = Q_BYTES + 2 * KV_STAGES * KV_BYTES + P_BYTES + 256;
+    const int smem = Q_BYTES + 2 * KV_STAGES * KV_BYTES + P_BYTES + 1024;  // 113 KB: two CTAs to an SM, to the byte
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attn_prefill_tc_kernel<<<dim3(n_tiles, n_heads), FA_THREADS, smem, (cudaStream_t)stream>>>(qm, km, vm, p);
+    abk_launch(attn_prefill_tc_kernel, dim3(n_tiles, n_heads), dim3(FA_THREADS), smem, (cudaStream_t)stream, qm, km, vm, p);
     return ABK_LAUNCH_RESULT();
 }

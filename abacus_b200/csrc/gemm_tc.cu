@@ -17,6 +17,10 @@
 // tile to scratch memory and takes a ticket; the last one adds the partials in split order
 // (so the result does not depend on which CTA came last) and stores the tile.
 //
+// Many rows and many tiles (a prompt): the persistent kernel below. One CTA to an SM walks over the
+// tiles; tensor memory holds two accumulators, so the four epilogue warps store tile i while the
+// tensor cores are on tile i + 1, and the ring of stages never drains between tiles.
+//
 // K may be any multiple of 8 (a TMA row pitch must be a multiple of 16 bytes); rows beyond M or
 // N and columns beyond K are zero-filled by TMA. Other shapes are refused, not approximated.
 // Formula: src/model.c:299, 302, 307, 309, 324.
@@ -213,6 +217,135 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
     }
 }
 
+// ------------------------------------------------------------------ persistent kernel for many tiles
+// Tile t is rows (t % m_tiles) * 128 and columns (t / m_tiles) * BN; CTA c takes tiles c, c + grid, ...
+// Warp 0 loads, warp 1 issues the products into accumulator (i & 1) of its i-th tile, warps 2-5 store
+// the accumulator of the tile before. acc_full / acc_empty hand the two accumulators back and forth.
+template <int BN, int STAGES, typename TO>
+__global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p,
+                                                                          const __grid_constant__ CUtensorMap map_q,
+                                                                          GemmTc g, int m_tiles, int tiles) {
+    using S = GemmSmem<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *a_tiles = smem, *b_tiles = smem + STAGES * S::A_BYTES;
+    uint64_t *full = (uint64_t *)(smem + STAGES * (S::A_BYTES + S::B_BYTES));
+    uint64_t *empty = full + STAGES, *acc_full = empty + STAGES, *acc_empty = acc_full + 2;
+    uint32_t *tmem_holder = (uint32_t *)(acc_empty + 2);
+    volatile int *flags = (volatile int *)(tmem_holder + 1);  // [0]: a wait ran out
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) tc::mbar_init(&full[s], 1), tc::mbar_init(&empty[s], 1);
+        for (int b = 0; b < 2; b++) tc::mbar_init(&acc_full[b], 1), tc::mbar_init(&acc_empty[b], 4);
+        flags[0] = 0;
+        tc::mbar_init_fence();
+        tc::tma_prefetch_map(&map_p), tc::tma_prefetch_map(&map_q);
+    }
+    if (warp == 1) tc::tmem_alloc(tmem_holder, TMEM_COLS);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem = *tmem_holder;
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int t = blockIdx.x; t < tiles && !flags[0]; t += gridDim.x) {
+                const int p0 = (t % m_tiles) * TILE_P, q0 = (t / m_tiles) * BN;
+                for (int kb = 0; kb < g.k_blocks; kb++, issued++) {
+                    int s = issued % STAGES;
+                    if (!tc::mbar_wait(&empty[s], ((issued / STAGES) & 1) ^ 1)) {
+                        flags[0] = 1;
+                        break;
+                    }
+                    tc::mbar_expect_tx(&full[s], S::A_BYTES + S::B_BYTES);
+                    tc::tma_load_2d(a_tiles + s * S::A_BYTES, &map_p, kb * TILE_K, p0, &full[s]);
+                    tc::tma_load_2d(b_tiles + s * S::B_BYTES, &map_q, kb * TILE_K, q0, &full[s]);
+                }
+            }
+            if (flags[0]) {  // let the copies still in flight land before the CTA's memory goes away
+                for (int i = max(0, issued - STAGES); i < issued; i++) tc::mbar_wait(&full[i % STAGES], (i / STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::idesc_bf16_f32(TILE_P, BN);
+            int done = 0, it = 0;
+            for (int t = blockIdx.x; t < tiles && !flags[0]; t += gridDim.x, it++) {
+                const int b = it & 1;
+                if (!tc::mbar_wait(&acc_empty[b], ((it >> 1) & 1) ^ 1)) {  // the epilogue is done with this accumulator
+                    flags[0] = 1;
+                    break;
+                }
+                tc::fence_after_sync();
+                for (int kb = 0; kb < g.k_blocks; kb++, done++) {
+                    int s = done % STAGES;
+                    if (!tc::mbar_wait(&full[s], (done / STAGES) & 1)) {
+                        flags[0] = 1;
+                        break;
+                    }
+                    tc::fence_after_sync();
+                    uint32_t a = tc::smem_addr(a_tiles + s * S::A_BYTES), bq = tc::smem_addr(b_tiles + s * S::B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TILE_K / 16; k++)
+                        tc::mma_ss(tmem + b * BN, tc::smem_desc_k_sw128(a + k * 32), tc::smem_desc_k_sw128(bq + k * 32), idesc,
+                                   kb > 0 || k > 0);
+                    tc::mma_commit(&empty[s]);
+                }
+                if (flags[0]) break;
+                tc::mma_commit(&acc_full[b]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3, row = quarter * 32 + lane;
+        TO *out = (TO *)g.out;
+        int it = 0;
+        for (int t = blockIdx.x; t < tiles; t += gridDim.x, it++) {
+            const int b = it & 1;
+            const int p = (t % m_tiles) * TILE_P + row, q0 = (t / m_tiles) * BN;
+            // every lane takes the same way out: the loads from tensor memory below are for whole warps
+            const bool ok = __all_sync(0xffffffffu, !flags[0] && tc::mbar_wait(&acc_full[b], (it >> 1) & 1));
+            if (!ok) {
+                flags[0] = 1;
+                break;
+            }
+            tc::fence_after_sync();
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c0, v);
+                tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c0 + 16, v + 16);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int h = 0; h < 32; h += 16) {
+                    if (g.vec && p < g.P && q0 + c0 + h + 16 <= g.Q) {
+                        store16(out + (long long)p * g.stride_p + q0 + c0 + h, v + h);
+                    } else if (p < g.P) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (q0 + c0 + h + j < g.Q)
+                                out[(long long)p * g.stride_p + (long long)(q0 + c0 + h + j) * g.stride_q] =
+                                    from_float<TO>(__uint_as_float(v[h + j]));
+                    }
+                }
+            }
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&acc_empty[b]);
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (flags[0] && threadIdx.x == 0) atomicOr(g.status + 1, 1);
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_free(tmem, TMEM_COLS);
+    }
+}
+
 // ------------------------------------------------------------------ host side
 
 typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -289,6 +422,21 @@ static int launch(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g,
     return ABK_LAUNCH_RESULT();
 }
 
+template <int BN, int STAGES, typename TO>
+static int launch_persistent(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g, int m_tiles, int tiles,
+                             cudaStream_t s) {
+    auto kernel = gemm_tc_persistent_kernel<BN, STAGES, TO>;
+    static bool configured = false;
+    constexpr int bytes = GemmSmem<BN, STAGES>::BYTES;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    abk_launch(kernel, dim3(tiles < 148 ? tiles : 148), dim3(GEMM_THREADS), (size_t)bytes, s, mp, mq, g, m_tiles, tiles);
+    return ABK_LAUNCH_RESULT();
+}
+
 template <typename TO>
 static int launch_bn(int bn, const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g, dim3 grid, cudaStream_t s) {
     switch (bn) {
@@ -308,10 +456,10 @@ extern "C" int abk_gemm_tc_scratch_tickets() { return 1 << 16; }
 // x [M, K] and w [N, K] bfloat16 with row pitches ldx, ldw (elements); out [M, N] bfloat16 or
 // float32 with row pitch ldo. scratch: float32 [abk_gemm_tc_scratch_floats()]; tickets: int32
 // [abk_gemm_tc_scratch_tickets()], all zero; status: int32 [>= 2], word 1 is set if a wait ran out.
-// force_bn / force_swap / force_splits (0 / -1 / 0: choose) pin the configuration, for tests.
+// force_bn / force_swap / force_splits / force_persistent (0 / -1 / 0 / -1: choose) pin the configuration, for tests.
 extern "C" int abk_gemm_tc(const void *x, const void *w, void *out, int out_dtype, int M, int N, int K, long long ldx,
                            long long ldw, long long ldo, float *scratch, int *tickets, int *status, int force_bn,
-                           int force_swap, int force_splits, void *stream) {
+                           int force_swap, int force_splits, int force_persistent, void *stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8)
         ABK_REFUSE("gemm_tc: K = %d and the row pitches %lld, %lld must be multiples of 8", K, ldx, ldw);
@@ -325,6 +473,13 @@ extern "C" int abk_gemm_tc(const void *x, const void *w, void *out, int out_dtyp
         bn = N > 128 && tiles256 >= 148 ? 256 : N > 64 ? 128 : 64;
     }
     if (force_bn) bn = force_bn;
+    // many rows: the persistent kernel, column tiles of 256 if that still gives most SMs a tile, else of 128
+    // (with a very long K two CTAs of the other kernel on an SM, each other's stalls covered, were measured faster)
+    bool persistent = !swap && M > 256 && N >= 128 && K <= 4096 &&
+                      (long long)((M + TILE_P - 1) / TILE_P) * ((N + 127) / 128) >= 96;
+    if (force_persistent >= 0) persistent = force_persistent != 0 && !swap;
+    if (persistent && !force_bn) bn = (long long)((M + TILE_P - 1) / TILE_P) * ((N + 255) / 256) >= 112 ? 256 : 128;
+    if (persistent && bn != 128 && bn != 256) ABK_REFUSE("gemm_tc: the persistent kernel has column tiles of 128 and 256, not %d", bn);
     int P = swap ? N : M, Q = swap ? M : N;
     if (swap && M > bn && M > 256) ABK_REFUSE("gemm_tc: %d rows do not fit the swapped layout", M);
     dim3 grid((P + TILE_P - 1) / TILE_P, (Q + bn - 1) / bn, 1);
@@ -338,6 +493,7 @@ extern "C" int abk_gemm_tc(const void *x, const void *w, void *out, int out_dtyp
         if (splits < 1) splits = 1;
     }
     if (force_splits) splits = force_splits;
+    if (persistent) splits = 1;
     if (splits > k_blocks) splits = k_blocks;
     int per = (k_blocks + splits - 1) / splits;
     splits = (k_blocks + per - 1) / per;
@@ -362,6 +518,13 @@ extern "C" int abk_gemm_tc(const void *x, const void *w, void *out, int out_dtyp
     g.vec = !swap && ((uintptr_t)out % 16 == 0) && (ldo * esize) % 16 == 0;
     cudaStream_t s = (cudaStream_t)stream;
     const CUtensorMap &mp = swap ? mw : mx, &mq = swap ? mx : mw;
+    if (persistent) {
+        const int m_tiles = grid.x, tiles = grid.x * grid.y;
+        if (bn == 256) return out_dtype == ABK_BF16 ? launch_persistent<256, 4, __nv_bfloat16>(mp, mq, g, m_tiles, tiles, s)
+                                                    : launch_persistent<256, 4, float>(mp, mq, g, m_tiles, tiles, s);
+        return out_dtype == ABK_BF16 ? launch_persistent<128, 6, __nv_bfloat16>(mp, mq, g, m_tiles, tiles, s)
+                                     : launch_persistent<128, 6, float>(mp, mq, g, m_tiles, tiles, s);
+    }
     if (out_dtype == ABK_BF16) rc = launch_bn<__nv_bfloat16>(bn, mp, mq, g, grid, s);
     else rc = launch_bn<float>(bn, mp, mq, g, grid, s);
     if (rc == ABK_REFUSED) ABK_REFUSE("gemm_tc: no kernel for a column tile of %d", bn);

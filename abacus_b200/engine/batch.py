@@ -37,10 +37,11 @@ class StepBatch:
             self._host = self._host.pin_memory()
         self._dev = torch.zeros(int(offsets[-1]), dtype=torch.int32, device=self.device)
         names = ["tokens", "token_seq", "token_pos", "seq_slot", "seq_start", "seq_pos0", "seq_len_after", "logit_rows"]
-        self._h = {}
+        self._h, self._parts = {}, {}
         for name, off, size in zip(names, offsets[:-1], sizes):
             self._h[name] = self._host[int(off):int(off) + size].numpy()
-            setattr(self, name, self._dev[int(off):int(off) + size])
+            self._parts[name] = self._dev[int(off):int(off) + size]
+            setattr(self, name, self._parts[name])
         self.n_rows = n_rows
         self.n_tokens = self.n_seqs = self.n_logit_rows = 0
         self.max_position = 0
@@ -49,10 +50,12 @@ class StepBatch:
         self.any_continuation = False
         self._sent = None
 
-    def fill(self, sequences, pad_logits=False):
+    def fill(self, sequences, pad_logits=False, exact=False):
         """Write the step described by `sequences` (list of Sequence) and send it to the device.
         pad_logits: logits are made for as many rows as this StepBatch has room for (a captured graph
-        needs a fixed number); the rows beyond the wanted ones repeat row 0 and are ignored."""
+        needs a fixed number); the rows beyond the wanted ones repeat row 0 and are ignored.
+        exact: the step has as many rows, sequences and logit rows as `sequences` bring, not as many as
+        there is room for (an engine keeps one StepBatch for steps of every size)."""
         h = self._h
         if self._sent is not None:
             self._sent.synchronize()  # the last copy must have read the host buffer before it is rewritten
@@ -87,6 +90,13 @@ class StepBatch:
         self.n_tokens, self.n_seqs, self.n_logit_rows = n_tokens, len(sequences), n_logits
         if pad_logits:
             self.n_logit_rows = self.cap_logits
+        if exact:
+            self.n_rows = n_tokens
+            n_seqs = len(sequences)
+            for name, n in (("tokens", n_tokens), ("token_seq", n_tokens), ("token_pos", n_tokens), ("seq_slot", n_seqs),
+                            ("seq_start", n_seqs + 1), ("seq_pos0", n_seqs), ("seq_len_after", n_seqs),
+                            ("logit_rows", max(1, n_logits))):
+                setattr(self, name, self._parts[name][:n])
         self.sequences = list(sequences)  # host view, for mixers that walk the sequences themselves
         self._tiles_key = None
         self.max_position = max((s.start + len(s.tokens) - 1 for s in sequences), default=0)
@@ -103,10 +113,13 @@ class StepBatch:
         """(sequence, first row among its new tokens) for every tile of `rows_per_tile` query rows of the
         step, as an int32 tensor [tiles, 2] on the device: the work list of the prefill attention kernel."""
         if getattr(self, "_tiles_key", None) != rows_per_tile:  # fill() resets it
-            pairs = [(i, r) for i, s in enumerate(self.sequences) for r in range(0, len(s.tokens), rows_per_tile)]
+            seq = np.concatenate([np.full(-(-len(s.tokens) // rows_per_tile), i, dtype=np.int32)
+                                  for i, s in enumerate(self.sequences)])
+            row = np.concatenate([np.arange(0, len(s.tokens), rows_per_tile, dtype=np.int32) for s in self.sequences])
+            keys = np.array([s.start for s in self.sequences], dtype=np.int64)[seq] + row
             # tiles that see the most keys first: the long ones start early and the short ones fill the tail
-            pairs.sort(key=lambda ir: -(self.sequences[ir[0]].start + ir[1]))
-            self._tiles = torch.tensor(pairs, dtype=torch.int32).reshape(-1, 2).to(self.device)
+            order = np.argsort(-keys, kind="stable")
+            self._tiles = torch.from_numpy(np.stack([seq[order], row[order]], axis=1)).to(self.device)
             self._tiles_key = rows_per_tile
         return self._tiles
 

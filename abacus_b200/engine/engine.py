@@ -8,6 +8,8 @@ sequence. This is abacus's forward(tokens, n, pos, logits, n_logits)
 """
 import os
 
+import numpy as np
+
 import torch
 
 from ..cache import SequenceCache
@@ -58,6 +60,7 @@ class Engine:
         # from the step's contents cannot be captured. Parts say so with `capturable = True`.
         capturable = all(getattr(part, "capturable", False) for b in model.blocks for part in b.parts().values())
         self.graphs = DecodeGraphs(self) if use_graphs and capturable else None
+        self._step_batch = None
 
     # ------------------------------------------------------------ sequences
     def open(self):
@@ -83,12 +86,12 @@ class Engine:
             if slot in seen:
                 raise StepError(f"slot {slot} appears twice in one step")
             seen.add(slot)
-            tokens = [int(t) for t in tokens]
-            if not tokens:
+            tokens = np.asarray(tokens, dtype=np.int64).reshape(-1)
+            if not tokens.size:
                 raise StepError(f"slot {slot}: a step must bring at least one token")
-            bad = [t for t in tokens if not 0 <= t < self.vocab]
-            if bad:
-                raise StepError(f"slot {slot}: token {bad[0]} is outside the vocabulary of {self.vocab}")
+            if tokens.min() < 0 or tokens.max() >= self.vocab:
+                bad = tokens[(tokens < 0) | (tokens >= self.vocab)]
+                raise StepError(f"slot {slot}: token {int(bad[0])} is outside the vocabulary of {self.vocab}")
             seqs.append(Sequence(slot, tokens, self.cache.length[slot], [int(w) for w in want]))
         for s in seqs:
             self.cache.reserve(s.slot, s.start + len(s.tokens))
@@ -103,13 +106,24 @@ class Engine:
             logits = graph.run(seqs)
             self.last_batch = graph.batch
         else:
-            n_rows = sum(len(s.tokens) for s in seqs)
-            batch = StepBatch(n_rows, len(seqs), sum(len(s.want) for s in seqs), self.model.ctx.device).fill(seqs)
+            batch = self._room_for(sum(len(s.tokens) for s in seqs), len(seqs), sum(len(s.want) for s in seqs))
+            batch.fill(seqs, exact=True)
             logits = self.model.forward(batch, self.cache)
             self.last_batch = batch
         for s in seqs:
             self.cache.advance(s.slot, len(s.tokens))
         return logits
+
+    def _room_for(self, n_rows, n_seqs, n_logits):
+        """The engine's StepBatch for steps outside a graph; replaced by a larger one when a step outgrows it
+        (pinned memory is slow to get, so it is not made anew for every step)."""
+        b = self._step_batch
+        if b is None or n_rows > b.cap_rows or n_seqs > b.cap_seqs or n_logits > b.cap_logits:
+            grow = lambda n, least: max(least, 1 << max(0, int(n) - 1).bit_length())
+            b = StepBatch(grow(max(n_rows, b.cap_rows if b else 0), 256), grow(max(n_seqs, b.cap_seqs if b else 0), 16),
+                          grow(max(n_logits, b.cap_logits if b else 0), 64), self.model.ctx.device)
+            self._step_batch = b
+        return b
 
     def check_status(self):
         """Raise if a kernel reported a fault (a bounded wait that ran out, a token out of range)."""

@@ -107,13 +107,14 @@ def bench_gemm(args):
         xs, wn = torch.randn(args.m, args.k, device="cuda"), torch.ones(args.k, device="cuda")
         fns = []
         for w in ws:
-            fns.append(lambda w=w: ops.gemm_tc(x, w, out, tile_n=args.tile_n, swap=args.swap, splits=args.splits))
+            fns.append(lambda w=w: ops.gemm_tc(x, w, out, tile_n=args.tile_n, swap=args.swap, splits=args.splits,
+                                                   persistent=args.persistent))
             fns.append(lambda: ops.add_rmsnorm(xs, None, wn, x, 1e-6))
         us, best = timed_graph(fns)
         us, best = 2 * us, 2 * best  # per pair
     else:
         us, best = timed_graph([lambda w=w: ops.gemm_tc(x, w, out, tile_n=args.tile_n, swap=args.swap,
-                                                        splits=args.splits) for w in ws])
+                                                        splits=args.splits, persistent=args.persistent) for w in ws])
     nbytes = (args.m * args.k + args.n * args.k) * 2 + out.numel() * out.element_size()
     flops = 2.0 * args.m * args.n * args.k
     return {"kernel": "gemm_tc", "m": args.m, "n": args.n, "k": args.k, "us": round(us, 2), "best_us": round(best, 2),
@@ -200,6 +201,7 @@ def main(argv=None):
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--swap", type=int, default=-1)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--persistent", type=int, default=-1, help="gemm: 1 / 0 pins the persistent kernel on / off")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2176)
     ap.add_argument("--tokens", type=int, default=2048)

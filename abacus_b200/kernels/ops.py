@@ -35,7 +35,9 @@ def _p(t):
 
 
 def _stream():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # torch's current stream as a raw handle (the public torch.cuda.current_stream() builds a Stream object
+    # for it and takes fifty times as long: a few microseconds on every launch)
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
 
 def _need_cuda(*tensors):
@@ -409,10 +411,11 @@ def gemm_tc_takes(x, w, out):
             and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1)
 
 
-def gemm_tc(x, w, out, m=None, tile_n=0, swap=-1, splits=0):
+def gemm_tc(x, w, out, m=None, tile_n=0, swap=-1, splits=0, persistent=-1):
     """out[:m] = x[:m] . w^T in bfloat16 on the tcgen05 tensor cores, float32 accumulation.
 
-    tile_n, swap and splits pin the tile configuration (tests); 0 / -1 / 0 let the kernel choose.
+    tile_n, swap, splits and persistent pin the tile configuration (tests); 0 / -1 / 0 / -1 let the
+    kernel choose.
     """
     _need_cuda(x, w, out)
     lib = load_module("gemm_tc")
@@ -424,4 +427,4 @@ def gemm_tc(x, w, out, m=None, tile_n=0, swap=-1, splits=0):
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
     _check(lib, lib.abk_gemm_tc(_p(x), _p(w), _p(out), _i(_dt(out)), _i(m), _i(n), _i(k), _ll(x.stride(0)),
                                 _ll(w.stride(0)), _ll(out.stride(0)), _p(sc.gemm_floats), _p(sc.gemm_tickets),
-                                _p(sc.status), _i(tile_n), _i(swap), _i(splits), _stream()), "gemm_tc")
+                                _p(sc.status), _i(tile_n), _i(swap), _i(splits), _i(persistent), _stream()), "gemm_tc")

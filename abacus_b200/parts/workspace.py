@@ -12,8 +12,12 @@ class Workspace:
         self.device = device
         self.generation = 0
         self._buffers = {}
+        self._views = {}
 
     def get(self, name, shape, dtype):
+        view = self._views.get((name, shape, dtype)) if type(shape) is tuple else None
+        if view is not None:
+            return view
         count = 1
         for s in shape:
             count *= int(s)
@@ -23,7 +27,13 @@ class Workspace:
             buf = torch.empty(max(count, 1), dtype=dtype, device=self.device)
             self._buffers[key] = buf
             self.generation += 1
-        return buf[:count].view(*shape)
+            self._views = {k: v for k, v in self._views.items() if (k[0], k[2]) != key}
+        view = buf[:count].view(*shape)
+        if type(shape) is tuple:
+            if len(self._views) > 4096:
+                self._views.clear()
+            self._views[(name, shape, dtype)] = view
+        return view
 
     def bytes(self):
         return sum(b.numel() * b.element_size() for b in self._buffers.values())

@@ -315,8 +315,20 @@ def test_gemm_tc_every_tile_configuration(ops, out_dtype):
     assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
 
 
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tc_persistent_kernel(ops, out_dtype):
+    """The kernel for many rows: both column tiles; fewer tiles than SMs, and so many that a CTA walks over
+    several and both accumulators come round again (165 and 330 tiles); ragged edges in M, N and K; a K
+    shorter than the ring of stages."""
+    rng = np.random.default_rng(23)
+    for tile_n, (m, n, k) in [(256, (300, 520, 72)), (128, (300, 520, 72)), (256, (1300, 3600, 136)),
+                              (128, (1300, 3600, 136)), (256, (2048, 1024, 1032)), (128, (257, 128, 8))]:
+        _gemm_case(ops, m, n, k, out_dtype, rng, tile_n=tile_n, persistent=1)
+    assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
+
+
 @pytest.mark.parametrize("m, n, k", [(1, 128, 64), (1, 1024, 2048), (8, 4096, 1024), (64, 1000, 72), (65, 192, 96),
-                                      (300, 389, 96), (2048, 1024, 1024), (5, 151936, 128), (130, 70, 8)])
+                                      (300, 389, 96), (2048, 1024, 1024), (5, 151936, 128), (130, 70, 8), (1500, 4096, 264)])
 def test_gemm_tc_chosen_configuration(ops, m, n, k):
     rng = np.random.default_rng(m + n + k)
     _gemm_case(ops, m, n, k, torch.float32, rng)
