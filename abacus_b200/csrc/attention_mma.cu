@@ -43,6 +43,7 @@ __global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(const __grid_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seq = p.tiles[2 * blockIdx.x], row0 = p.tiles[2 * blockIdx.x + 1], h = blockIdx.y;
+    if (seq < 0) return;  // padding of the work list (a captured step has a fixed number of tiles)
     const int kvh = h / (p.n_heads / p.n_kv_heads);
     const int start = p.seq_start[seq], pos0 = p.seq_pos0[seq], n_new = p.seq_len_after[seq] - pos0;
     const int last_row = min(row0 + PAGE - 1, n_new - 1);

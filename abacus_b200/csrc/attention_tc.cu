@@ -113,6 +113,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __
     // Before pdl_wait(): what kernels further back than the one just before this wrote (the step's index arrays,
     // the page table), and the CTA's own set-up. The loads that do not depend on one another go out together.
     const int seq = p.tiles[2 * blockIdx.x], row0 = p.tiles[2 * blockIdx.x + 1], h = blockIdx.y;
+    if (seq < 0) return;  // padding of the work list (a captured step has a fixed number of tiles)
     // an earlier CTA gave up on a wait: do not queue up behind it (one thread looks, so that all decide alike)
     if (threadIdx.x == 0) {
         *(volatile int *)swap = *(volatile int *)(p.status + 3);
@@ -372,11 +373,11 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __
         tc::tmem_free(tmem, 256);
     }
 #ifdef ABK_TRACE
-    if (threadIdx.x == 0) {  // every CTA's life: begin, end, its tile and head, its steps and its SM
+    if (threadIdx.x == 0) {  // every CTA's life: begin, end, its tile and head, its steps and its SM + 1 (a launch's record has 0 there)
         unsigned int i = atomicAdd(&abk_trace_count, 1u), sm;
         asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
         if (i < ABK_TRACE_MAX)
-            abk_trace_records[i] = {trace_begin, abk_trace_ns(), ABK_TRACE, (int)(blockIdx.x + (blockIdx.y << 16)), n_steps, (int)sm};
+            abk_trace_records[i] = {trace_begin, abk_trace_ns(), ABK_TRACE, (int)(blockIdx.x + (blockIdx.y << 16)), n_steps, (int)sm + 1};
     }
 #endif
 }

@@ -280,70 +280,83 @@ template <typename T> __global__ void qkv_prep_kernel(QkvPrep p) {
 template <int N> struct __align__(2 * N) Bf16Pack { __nv_bfloat16 v[N]; };
 #define FAST_WARPS 8
 
+#define FAST_HEADS 4  // heads a warp has in flight at a time
 template <int EPH> __global__ void __launch_bounds__(FAST_WARPS * 32) qkv_prep_fast_kernel(QkvPrep p) {
     constexpr int HD = 64 * EPH, HALF = 32 * EPH;
     typedef Bf16Pack<EPH> Pack;
-    // Everything but the row itself (the step's index arrays, the page table, the norm's weights, the
-    // angles) was written by kernels further back than the one just before this, and is read before pdl_wait().
+    // A CTA takes one token; its warps share the token's heads (q, then k, then v), FAST_HEADS at a time so
+    // that their loads are in flight together. Everything but the rows themselves (the step's index arrays,
+    // the page table, the norms' weights, the angles) was written by kernels further back than the one just
+    // before this, and is read before pdl_wait(), once per token instead of once per head.
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int head = blockIdx.y * FAST_WARPS + warp;
     const int total_heads = p.n_heads + 2 * p.n_kv_heads;
-    if (head >= (p.q_only ? p.n_heads : total_heads)) return;
+    const int n_work = p.q_only ? p.n_heads : total_heads;
     const int seq = p.token_seq[t];
     if (seq < 0) return;
     const int pos = p.token_pos[t];
-    __nv_bfloat16 *row = (__nv_bfloat16 *)p.qkv + ((long long)t * total_heads + head) * HD + lane * EPH;
-    const bool is_q = head < p.n_heads, is_k = !is_q && head < p.n_heads + p.n_kv_heads;
-    const int kv_head = is_q ? 0 : is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
-    const float *w = is_q ? p.q_norm : p.k_norm;
-    float w_lo[EPH], w_hi[EPH], cs[EPH], sn[EPH];
-    if ((is_q || is_k) && w) {
+    float wq_lo[EPH], wq_hi[EPH], wk_lo[EPH], wk_hi[EPH], cs[EPH], sn[EPH];
 #pragma unroll
-        for (int e = 0; e < EPH; e++) w_lo[e] = w[lane * EPH + e], w_hi[e] = w[HALF + lane * EPH + e];
+    for (int e = 0; e < EPH; e++) {
+        wq_lo[e] = p.q_norm ? p.q_norm[lane * EPH + e] : 1.0f, wq_hi[e] = p.q_norm ? p.q_norm[HALF + lane * EPH + e] : 1.0f;
+        wk_lo[e] = p.k_norm ? p.k_norm[lane * EPH + e] : 1.0f, wk_hi[e] = p.k_norm ? p.k_norm[HALF + lane * EPH + e] : 1.0f;
+        cs[e] = p.cos ? p.cos[(long long)pos * HALF + lane * EPH + e] : 1.0f;
+        sn[e] = p.sin ? p.sin[(long long)pos * HALF + lane * EPH + e] : 0.0f;
     }
-    if ((is_q || is_k) && p.cos) {
-        const float *c = p.cos + (long long)pos * HALF + lane * EPH, *sp = p.sin + (long long)pos * HALF + lane * EPH;
-#pragma unroll
-        for (int e = 0; e < EPH; e++) cs[e] = c[e], sn[e] = sp[e];
-    }
-    __nv_bfloat16 *dst = nullptr;  // where the key or value goes in the cache, if it is kept
-    if (!is_q && p.k_pool &&
-        !(p.cache.ring_pages > 0 && pos + p.cache.ring_pages * p.cache.tokens_per_page <= p.seq_len_after[seq] - 1)) {
-        const int page = cache_page(p.cache, p.seq_slot[seq], pos);
-        dst = (__nv_bfloat16 *)(is_k ? p.k_pool : p.v_pool) + cache_offset(p.cache, page, kv_head, p.n_kv_heads, pos, HD) +
-              lane * EPH;
-    }
+    long long kept_at = -1;  // where the token's keys and values go in the pools (kv head 0), if they are kept
+    if (!p.q_only && p.k_pool &&
+        !(p.cache.ring_pages > 0 && pos + p.cache.ring_pages * p.cache.tokens_per_page <= p.seq_len_after[seq] - 1))
+        kept_at = cache_offset(p.cache, cache_page(p.cache, p.seq_slot[seq], pos), 0, p.n_kv_heads, pos, HD);
+    __nv_bfloat16 *row0 = (__nv_bfloat16 *)p.qkv + (long long)t * total_heads * HD + lane * EPH;
     pdl_wait();
-    Pack lo = *(const Pack *)row, hi = *(const Pack *)(row + HALF);
-    if (is_q || is_k) {
-        float a[EPH], b[EPH], ss = 0.0f;
+    for (int h0 = warp; h0 < n_work; h0 += FAST_WARPS * FAST_HEADS) {
+        Pack lo[FAST_HEADS], hi[FAST_HEADS];
 #pragma unroll
-        for (int e = 0; e < EPH; e++) {
-            a[e] = __bfloat162float(lo.v[e]), b[e] = __bfloat162float(hi.v[e]);
-            ss += a[e] * a[e] + b[e] * b[e];
+        for (int u = 0; u < FAST_HEADS; u++) {
+            const int head = h0 + u * FAST_WARPS;
+            if (head < n_work) lo[u] = *(const Pack *)(row0 + (long long)head * HD), hi[u] = *(const Pack *)(row0 + (long long)head * HD + HALF);
         }
-        if (w) {
-            ss = warp_sum(ss);
-            const float scale = 1.0f / sqrtf(ss / (float)HD + p.eps);
 #pragma unroll
-            for (int e = 0; e < EPH; e++) {
-                a[e] = w_lo[e] * (a[e] * scale);
-                b[e] = w_hi[e] * (b[e] * scale);
+        for (int u = 0; u < FAST_HEADS; u++) {
+            const int head = h0 + u * FAST_WARPS;
+            if (head >= n_work) break;
+            const bool is_q = head < p.n_heads, is_k = !is_q && head < p.n_heads + p.n_kv_heads;
+            const int kv_head = is_q ? 0 : is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
+            if (is_q || is_k) {
+                float a[EPH], b[EPH], ss = 0.0f;
+#pragma unroll
+                for (int e = 0; e < EPH; e++) {
+                    a[e] = __bfloat162float(lo[u].v[e]), b[e] = __bfloat162float(hi[u].v[e]);
+                    ss += a[e] * a[e] + b[e] * b[e];
+                }
+                if (is_q ? p.q_norm != nullptr : p.k_norm != nullptr) {
+                    ss = warp_sum(ss);
+                    const float scale = 1.0f / sqrtf(ss / (float)HD + p.eps);
+#pragma unroll
+                    for (int e = 0; e < EPH; e++) {
+                        a[e] = (is_q ? wq_lo[e] : wk_lo[e]) * (a[e] * scale);
+                        b[e] = (is_q ? wq_hi[e] : wk_hi[e]) * (b[e] * scale);
+                    }
+                }
+                if (p.cos) {
+#pragma unroll
+                    for (int e = 0; e < EPH; e++) {
+                        float x = a[e], y = b[e];
+                        a[e] = x * cs[e] - y * sn[e];
+                        b[e] = y * cs[e] + x * sn[e];
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < EPH; e++) lo[u].v[e] = __float2bfloat16_rn(a[e]), hi[u].v[e] = __float2bfloat16_rn(b[e]);
+                __nv_bfloat16 *row = row0 + (long long)head * HD;
+                *(Pack *)row = lo[u], *(Pack *)(row + HALF) = hi[u];
+            }
+            if (!is_q && kept_at >= 0) {
+                __nv_bfloat16 *dst = (__nv_bfloat16 *)(is_k ? p.k_pool : p.v_pool) + kept_at +
+                                     (long long)kv_head * p.cache.tokens_per_page * HD + lane * EPH;
+                *(Pack *)dst = lo[u], *(Pack *)(dst + HALF) = hi[u];
             }
         }
-        if (p.cos) {
-#pragma unroll
-            for (int e = 0; e < EPH; e++) {
-                float x = a[e], y = b[e];
-                a[e] = x * cs[e] - y * sn[e];
-                b[e] = y * cs[e] + x * sn[e];
-            }
-        }
-#pragma unroll
-        for (int e = 0; e < EPH; e++) lo.v[e] = __float2bfloat16_rn(a[e]), hi.v[e] = __float2bfloat16_rn(b[e]);
-        *(Pack *)row = lo, *(Pack *)(row + HALF) = hi;
     }
-    if (dst) *(Pack *)dst = lo, *(Pack *)(dst + HALF) = hi;
 }
 
 extern "C" int abk_qkv_prep(void *qkv, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int q_only,
@@ -368,7 +381,7 @@ extern "C" int abk_qkv_prep(void *qkv, int dtype, int n_tokens, int n_heads, int
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == ABK_BF16 && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
         (!cos || (rotary_dim == head_dim && !interleaved)) && (uintptr_t)qkv % 16 == 0) {
-        dim3 fast((unsigned)n_tokens, (total_heads + FAST_WARPS - 1) / FAST_WARPS);
+        dim3 fast((unsigned)n_tokens);
         if (head_dim == 64) abk_launch(qkv_prep_fast_kernel<1>, fast, dim3(FAST_WARPS * 32), 0, s, p);
         else if (head_dim == 128) abk_launch(qkv_prep_fast_kernel<2>, fast, dim3(FAST_WARPS * 32), 0, s, p);
         else abk_launch(qkv_prep_fast_kernel<4>, fast, dim3(FAST_WARPS * 32), 0, s, p);

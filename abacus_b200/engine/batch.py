@@ -8,6 +8,8 @@ the host and sent to the device in one copy.
 
 Rows beyond the step's tokens (padding up to a fixed size, for a captured
 graph) carry sequence index -1; kernels skip them and no result depends on them.
+The same holds for the work lists of the prefill attention kernels (tiles of
+64 and of 128 query rows), which travel in the same buffer.
 """
 from dataclasses import dataclass
 
@@ -24,19 +26,25 @@ class Sequence:
     want: list  # places among `tokens` whose logits are wanted
 
 
+TILE_ROWS = (64, 128)  # query rows per tile of the prefill attention kernels
+
+
 class StepBatch:
     """Device-side index arrays of a step, with room for n_rows rows and n_seqs sequences."""
 
     def __init__(self, n_rows, n_seqs, n_logit_rows, device):
         self.device = torch.device(device)
         self.cap_rows, self.cap_seqs, self.cap_logits = n_rows, n_seqs, max(1, n_logit_rows)
+        self.cap_tiles = {r: n_rows // r + n_seqs + 1 for r in TILE_ROWS}  # no step of this size has more
         sizes = [n_rows, n_rows, n_rows, n_seqs, n_seqs + 1, n_seqs, n_seqs, self.cap_logits]
+        sizes += [2 * self.cap_tiles[r] for r in TILE_ROWS]
         offsets = np.concatenate([[0], np.cumsum([-(-s // 4) * 4 for s in sizes])])  # 16-byte aligned parts
         self._host = torch.zeros(int(offsets[-1]), dtype=torch.int32)
         if self.device.type == "cuda":
             self._host = self._host.pin_memory()
         self._dev = torch.zeros(int(offsets[-1]), dtype=torch.int32, device=self.device)
         names = ["tokens", "token_seq", "token_pos", "seq_slot", "seq_start", "seq_pos0", "seq_len_after", "logit_rows"]
+        names += [f"tiles{r}" for r in TILE_ROWS]
         self._h, self._parts = {}, {}
         for name, off, size in zip(names, offsets[:-1], sizes):
             self._h[name] = self._host[int(off):int(off) + size].numpy()
@@ -98,10 +106,14 @@ class StepBatch:
                             ("logit_rows", max(1, n_logits))):
                 setattr(self, name, self._parts[name][:n])
         self.sequences = list(sequences)  # host view, for mixers that walk the sequences themselves
-        self._tiles_key = None
+        self._tiles = {}
+        self.is_decode = all(len(s.tokens) == 1 for s in sequences)
+        for r in TILE_ROWS:
+            h[f"tiles{r}"][:] = -1
+            if not self.is_decode:
+                self._write_tiles(r, exact)
         self.max_position = max((s.start + len(s.tokens) - 1 for s in sequences), default=0)
         self.max_len_after = self.max_position + 1
-        self.is_decode = all(len(s.tokens) == 1 for s in sequences)
         self.any_continuation = any(s.start > 0 for s in sequences)
         self._dev.copy_(self._host, non_blocking=True)
         if self.device.type == "cuda":
@@ -109,19 +121,30 @@ class StepBatch:
             self._sent.record()
         return self
 
+    def _tiles_of(self, rows_per_tile):
+        """(sequence, first row among its new tokens) of every tile of `rows_per_tile` query rows, int32 [tiles, 2]."""
+        seq = np.concatenate([np.full(-(-len(s.tokens) // rows_per_tile), i, dtype=np.int32)
+                              for i, s in enumerate(self.sequences)])
+        row = np.concatenate([np.arange(0, len(s.tokens), rows_per_tile, dtype=np.int32) for s in self.sequences])
+        keys = np.array([s.start for s in self.sequences], dtype=np.int64)[seq] + row
+        # tiles that see the most keys first: the long ones start early and the short ones fill the tail
+        order = np.argsort(-keys, kind="stable")
+        return np.stack([seq[order], row[order]], axis=1)
+
+    def _write_tiles(self, rows_per_tile, exact):
+        name = f"tiles{rows_per_tile}"
+        tiles = self._tiles_of(rows_per_tile)
+        self._h[name][:tiles.size] = tiles.reshape(-1)
+        n = len(tiles) if exact else self.cap_tiles[rows_per_tile]  # a captured graph has a fixed number: the rest say -1
+        self._tiles[rows_per_tile] = self._parts[name][:2 * n].view(n, 2)
+
     def query_tiles(self, rows_per_tile=64):
-        """(sequence, first row among its new tokens) for every tile of `rows_per_tile` query rows of the
-        step, as an int32 tensor [tiles, 2] on the device: the work list of the prefill attention kernel."""
-        if getattr(self, "_tiles_key", None) != rows_per_tile:  # fill() resets it
-            seq = np.concatenate([np.full(-(-len(s.tokens) // rows_per_tile), i, dtype=np.int32)
-                                  for i, s in enumerate(self.sequences)])
-            row = np.concatenate([np.arange(0, len(s.tokens), rows_per_tile, dtype=np.int32) for s in self.sequences])
-            keys = np.array([s.start for s in self.sequences], dtype=np.int64)[seq] + row
-            # tiles that see the most keys first: the long ones start early and the short ones fill the tail
-            order = np.argsort(-keys, kind="stable")
-            self._tiles = torch.from_numpy(np.stack([seq[order], row[order]], axis=1)).to(self.device)
-            self._tiles_key = rows_per_tile
-        return self._tiles
+        """The work list of a prefill attention kernel: (sequence, first row among its new tokens) for every
+        tile of `rows_per_tile` query rows of the step, int32 [tiles, 2] on the device; a tile whose sequence is
+        -1 is padding. Tiles of 64 and 128 rows come with the step's one copy; other sizes are sent when asked for."""
+        if rows_per_tile not in self._tiles:
+            self._tiles[rows_per_tile] = torch.from_numpy(self._tiles_of(rows_per_tile)).to(self.device)
+        return self._tiles[rows_per_tile]
 
     def advance_on_device(self):
         """Every sequence moves one position on (a decode step follows a decode step); the tokens are

@@ -17,7 +17,7 @@ from ..config.registry import load_config
 from ..models.model import Model
 from ..weights.loader import load_folder
 from .batch import Sequence, StepBatch
-from .graphs import DecodeGraphs
+from .graphs import DecodeGraphs, PromptGraphs
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
           "f32": torch.float32}
@@ -60,6 +60,8 @@ class Engine:
         # from the step's contents cannot be captured. Parts say so with `capturable = True`.
         capturable = all(getattr(part, "capturable", False) for b in model.blocks for part in b.parts().values())
         self.graphs = DecodeGraphs(self) if use_graphs and capturable else None
+        prompts = use_graphs and capturable and os.environ.get("ABACUS_PROMPT_GRAPHS", "1") != "0"
+        self.prompt_graphs = PromptGraphs(self) if prompts else None
         self._step_batch = None
 
     # ------------------------------------------------------------ sequences
@@ -105,6 +107,8 @@ class Engine:
             graph = self.graphs.get(seqs)
             logits = graph.run(seqs)
             self.last_batch = graph.batch
+        elif self.prompt_graphs is not None and self.prompt_graphs.takes(seqs):  # a shape of prompts seen before
+            logits, self.last_batch = self.prompt_graphs.run(seqs)
         else:
             batch = self._room_for(sum(len(s.tokens) for s in seqs), len(seqs), sum(len(s.want) for s in seqs))
             batch.fill(seqs, exact=True)

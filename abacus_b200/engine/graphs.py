@@ -1,4 +1,4 @@
-"""Decode steps as captured CUDA graphs.
+"""Steps as captured CUDA graphs: decode steps, and steps that bring prompts.
 
 A decode step is a few hundred small kernels; launched one by one their launch cost exceeds
 their run time. So the step for a given number of rows (rounded up to a bucket, the rest
@@ -9,6 +9,12 @@ every row one position on, so that a loop can run without the host).
 
 A graph holds addresses: of the workspace, the cache, the rotary tables. If the workspace has
 grown since the capture (its generation changed), the graph is captured again.
+
+A step that brings prompts is a few hundred launches too, each costing the host some ten
+microseconds: for a small model that is as long as the GPU works on them. Such steps are captured per
+(rows, sequences, wanted rows), each rounded up to a bucket, the second time a shape comes by (a
+shape seen once is not worth a capture); the step's work lists for the attention kernels travel in
+the StepBatch like its other indices, so a replay needs nothing from the host but that one copy.
 """
 import gc
 
@@ -28,10 +34,10 @@ def row_bucket(n):
 
 
 class DecodeGraph:
-    def __init__(self, engine, rows, position_bound):
+    def __init__(self, engine, rows, position_bound, seqs=None, logit_rows=None):
         self.engine, self.rows, self.position_bound = engine, rows, position_bound
         device = engine.model.ctx.device
-        self.batch = StepBatch(rows, rows, rows, device)
+        self.batch = StepBatch(rows, rows if seqs is None else seqs, rows if logit_rows is None else logit_rows, device)
         self.batch.position_bound = position_bound
         self.graph = None
         self.generation = -1
@@ -64,13 +70,13 @@ class DecodeGraph:
         self.generation = model.ws.generation
 
     def run(self, sequences):
-        """Replay for this step's sequences (each with one token, logits wanted); returns the logits
-        of the first len(sequences) rows."""
+        """Replay for this step's sequences; returns the logits of its wanted rows (for a decode step: of
+        the first len(sequences) rows)."""
         if self.graph is None or self.generation != self.engine.model.ws.generation:
             self.capture(sequences)
         self.batch.fill(sequences, pad_logits=True)
         self.graph.replay()
-        return self.logits[:len(sequences)]
+        return self.logits[:sum(len(s.want) for s in sequences)]
 
     def replay_advanced(self):
         """Replay after moving every row one position on, on the device; the tokens are whatever the
@@ -99,3 +105,55 @@ class DecodeGraphs:
 
     def run(self, sequences):
         return self.get(sequences).run(sequences)
+
+
+def prompt_bucket(n):
+    """Rows of a captured prompt step: powers of two up to 128, then steps of an eighth to a sixteenth of the size."""
+    if n <= 128:
+        return max(16, 1 << (n - 1).bit_length())
+    step = max(128, 1 << (n.bit_length() - 4))
+    return -(-n // step) * step
+
+
+class PromptGraphs:
+    """Captured steps that bring several tokens of some sequence. A shape is captured when it comes by a
+    second time; at most `keep` graphs are kept (the least recently used goes)."""
+
+    def __init__(self, engine, keep=16):
+        self.engine, self.keep = engine, keep
+        self.graphs, self.seen = {}, {}
+        self.captured = self.replayed = 0
+        needs = [n for n in engine.model.cache_needs() if n is not None]
+        self.windowed = any(getattr(n, "window", None) for n in needs)
+
+    def key(self, sequences):
+        rows = sum(len(s.tokens) for s in sequences)
+        wanted = sum(len(s.want) for s in sequences)
+        return (prompt_bucket(rows), 1 << (len(sequences) - 1).bit_length(), 1 << max(0, wanted - 1).bit_length())
+
+    def takes(self, sequences):
+        """Whether this step is replayed (or captured now). Steps of one token per sequence are the decode
+        graphs' (or run as they are); a model with a window checks its steps on the host."""
+        if self.windowed or all(len(s.tokens) == 1 for s in sequences):
+            return False
+        key = self.key(sequences)
+        if key in self.graphs:
+            return True
+        self.seen[key] = self.seen.get(key, 0) + 1
+        if len(self.seen) > 4096:
+            self.seen.clear()
+        return self.seen[key] >= 2
+
+    def run(self, sequences):
+        key = self.key(sequences)
+        graph = self.graphs.pop(key, None)
+        if graph is None:
+            if len(self.graphs) >= self.keep:
+                self.graphs.pop(next(iter(self.graphs)))
+            graph = DecodeGraph(self.engine, key[0], None, seqs=key[1], logit_rows=key[2])
+        self.graphs[key] = graph  # most recently used last
+        fresh = graph.graph is None or graph.generation != self.engine.model.ws.generation
+        logits = graph.run(sequences)
+        self.captured += fresh
+        self.replayed += 1
+        return logits, graph.batch

@@ -22,8 +22,10 @@ class Record(ctypes.Structure):
                 ("grid", ctypes.c_int), ("block", ctypes.c_int), ("pad", ctypes.c_int)]
 
 
-def read(max_records=16384):
-    """All records made since the last call, over every loaded kernel library, ordered by release time."""
+def read(max_records=16384, lives=False):
+    """All records of launches made since the last call, over every loaded kernel library, ordered by
+    release time. lives=True: instead the records some kernels keep of every CTA's life (begin, end,
+    what it worked on: `grid`, how much: `block`, and on which SM)."""
     if not build.TRACE:
         raise RuntimeError("the kernel libraries are built without records: set ABACUS_TRACE=1 before importing")
     out = []
@@ -32,8 +34,8 @@ def read(max_records=16384):
         n = lib.abk_trace_read(buf, ctypes.c_int(max_records))
         if n < 0:
             raise RuntimeError(f"reading the records of {module} failed")
-        out += [dict(module=module, reached=r.reached, released=r.released, grid=r.grid, block=r.block)
-                for r in buf[:n]]
+        out += [dict(module=module, reached=r.reached, released=r.released, grid=r.grid, block=r.block, sm=r.pad - 1)
+                for r in buf[:n] if (r.pad != 0) == lives]
     return sorted(out, key=lambda r: r["released"])
 
 

@@ -187,8 +187,8 @@ def prefill(model, repeats=3):
     from abacus_b200.engine import Engine
     engine = Engine(model, max_tokens=CONTEXT, max_slots=1, max_context=CONTEXT)
     prompt = prompts_for(1, model.spec.vocab, 99)[0][:PREFILL_TOKENS]
-    times = []
-    for i in range(repeats + 1):
+    times, untimed = [], 2  # the first run loads the kernels, the second captures the step's graph
+    for i in range(repeats + untimed):
         slot = engine.open()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
@@ -196,7 +196,7 @@ def prefill(model, repeats=3):
         engine.step([(slot, prompt, [len(prompt) - 1])])
         end.record()
         torch.cuda.synchronize()
-        if i:
+        if i >= untimed:
             times.append(start.elapsed_time(end))
         engine.close(slot)
     engine.check_status()
@@ -213,6 +213,41 @@ def prefill(model, repeats=3):
     return ms, flops
 
 
+def timeline(model, batch):
+    """The launches of one decode step and of one 2,048-token prefill with the time each took inside its step
+    (from the records of abacus_b200/kernels/trace.py; the libraries must be built with ABACUS_TRACE=1)."""
+    import torch
+    from abacus_b200.engine import Engine
+    from abacus_b200.kernels import trace
+
+    def show(title, rows):
+        print(title)
+        for i, row in enumerate(rows):
+            # a launch's release comes when the launch before it is complete: the gap is that launch's time
+            took = rows[i + 1]["after_previous_us"] if i + 1 < len(rows) else float("nan")
+            print(f"  {row['module']:22s} grid {row['grid']:6d} x {row['block']:4d}  waited {row['waited_us']:6.2f} us"
+                  f"  took {took:7.2f} us")
+
+    device_decode(model, batch, 4, 3)
+    torch.cuda.synchronize()
+    trace.read()
+    device_decode(model, batch, 2, 0)
+    rows = trace.timeline(trace.read())
+    per_step = len(rows) // 3 if len(rows) >= 3 else len(rows)  # the prompts' step and two decode steps were recorded
+    show(f"decode step, batch {batch} (kernels without a dependency wait are not recorded)", rows[-per_step:])
+    engine = Engine(model, max_tokens=CONTEXT, max_slots=1, max_context=CONTEXT)
+    prompt = prompts_for(1, model.spec.vocab, 99)[0][:PREFILL_TOKENS]
+    for i in range(3):
+        slot = engine.open()
+        engine.step([(slot, prompt, [len(prompt) - 1])])
+        torch.cuda.synchronize()
+        engine.close(slot)
+        if i == 1:
+            trace.read()
+    show(f"prefill of {PREFILL_TOKENS} tokens", trace.timeline(trace.read()))
+    return 0
+
+
 def run_ours(args):
     import torch
     from abacus_b200.kernels import build_all
@@ -224,6 +259,8 @@ def run_ours(args):
     weight_bytes = model.weight_bytes_read_per_step()
     kv_token = kv_bytes_per_token(model)
 
+    if args.only == "timeline":  # with ABACUS_TRACE=1: what each launch of a decode step and of a prefill took, as they ran
+        return timeline(model, args.batch)
     if args.only == "prefill":  # for profiling: the prefill step alone
         pre_ms, pre_flops = prefill(model, repeats=1)
         print(json.dumps({"prefill_ms": round(pre_ms, 3), "frac": round(pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}))
@@ -323,7 +360,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"], help="run one part (for profiling)")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "timeline"],
+                    help="run one part (for profiling); timeline needs ABACUS_TRACE=1")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in config)")
     args = ap.parse_args()
     if args.gpus != 1:

@@ -166,6 +166,52 @@ def test_schedule_names_a_layer_twice_and_shares_a_cache(tmp_path, dname, dtype)
     assert_logits(np.concatenate(got), want, dname, "schedule")
 
 
+@pytest.mark.parametrize("dname, dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_prompt_steps_of_a_shape_seen_before_are_replayed(tmp_path, name, dname, dtype):
+    """A step that brings prompts is captured the second time its shape (rows, sequences, wanted rows, each
+    rounded up) comes by, and replayed after that. With other tokens, other lengths inside the same bucket and
+    other slots every replay gives what the plain implementation gives; and every step, also those in which
+    the sequences go on by several tokens, gives what an engine without graphs gives for it (the padding of a
+    captured step changes no result)."""
+    from abacus_b200.engine import Engine, load_model
+    folder = make_model_folder(tmp_path, name)
+    model = load_model(folder, dname)
+    engine, eager = Engine(model, max_tokens=4096), Engine(model, max_tokens=4096, use_graphs=False)
+    pcfg, pw = plain.load(folder)
+    rng = np.random.default_rng(11)
+
+    def want_and_noise(tokens):  # the plain logits in this dtype, and the rounding noise they carry (helpers.assert_logits)
+        exact = plain.forward(pcfg, pw, tokens)
+        if dtype == torch.bfloat16:
+            want = plain.forward(pcfg, pw, tokens, rnd=plain.bf16_round)
+            return want, float(np.abs(want - exact).max())
+        return exact, float(np.abs(exact - plain.forward64(pcfg, pw, tokens)).max())
+
+    def both(entries_of):
+        got = engine.step(entries_of(slots)).cpu().numpy()
+        ref = eager.step(entries_of(eager_slots)).cpu().numpy()
+        close = 1e-5 if dtype == torch.float32 else 4e-3  # of the largest logit: the same kernels on the same rows
+        assert np.abs(got - ref).max() <= close * np.abs(ref).max(), "a replayed step differs from the step run as it is"
+        return got
+
+    for round_, lengths in enumerate([(150, 70), (141, 90), (160, 60), (129, 101)]):  # 220-231 rows: one bucket
+        ids = [random_tokens(rng, n, pcfg["vocab"]) for n in lengths]
+        slots, eager_slots = [engine.open() for _ in lengths], [eager.open() for _ in lengths]
+        got = both(lambda ss: [(s, t, [0, len(t) - 1]) for s, t in zip(ss, ids)])
+        for i, t in enumerate(ids):
+            want, noise = want_and_noise(t)
+            assert_logits(got[2 * i:2 * i + 2], want[[0, len(t) - 1]], dname, f"{name} round {round_} sequence {i}", noise)
+        if round_ == 3:  # the sequences go on by several tokens each: another shape, met twice
+            for again in range(2):
+                more = [random_tokens(rng, 40, pcfg["vocab"]) for _ in lengths]
+                both(lambda ss: [(s, m, [39]) for s, m in zip(ss, more)])
+        for s, e in zip(slots, eager_slots):
+            engine.close(s), eager.close(e)
+    engine.check_status()
+    assert engine.prompt_graphs.captured == 2 and engine.prompt_graphs.replayed == 4 and eager.prompt_graphs is None
+
+
 # ------------------------------------------------------------------ generation through the entry point
 
 @pytest.mark.parametrize("dname", ["float32", "bfloat16"])
