@@ -1,8 +1,14 @@
 // Causal prefill attention on the 5th-generation tensor cores (tcgen05), head size 128, bfloat16
 // paged cache, no window.
 //
-// A CTA takes 128 query rows of one (sequence, head) and walks the pages of keys the last of its
-// rows may see, 64 keys at a time:
+// A CTA takes 128 query rows of one (sequence, head) and all pages of keys the last of the rows may see,
+// or, for a tile that sees many (the tiles of a prompt see from 1 to all of its pages, and a kernel lasts
+// as long as its longest CTA), the earlier or the later half of them: then both CTAs leave their partial
+// the CTA that is through first leaves its partial result (O, maximum, sum) in scratch memory, and the other
+// one adds the two, always in the same order, and stores the rows. (Pairs as thread-block clusters, with the partial
+// result handed over through distributed shared memory, were measured slower: a cluster needs a free
+// place on both SMs of a pair at once, and a sixth of the places stayed empty.) The CTAs run in the order
+// of the work list, longest first, all heads of an entry together. A CTA walks its pages 64 keys at a time:
 //   warp 0     TMA: the query tile once ([128, 128] as two swizzled boxes), then a page of keys and
 //              a page of values per step into a ring of three stages;
 //   warp 1     one thread issues tcgen05.mma: S = Q K^T (128 x 64, into one of two score buffers in
@@ -42,9 +48,15 @@ struct AttnTc {
     __nv_bfloat16 *out;  // [tokens, n_heads * HD]
     int n_heads, n_kv_heads;
     float scale_log2;
-    const int *tiles;  // [n_tiles][2]: sequence of the step, first of its 128 rows among the sequence's new tokens
-    const int *seq_start, *seq_pos0, *seq_len_after, *seq_slot;
+    // [n_work][8], a CTA's work: sequence of the step (-1: none), first of its 128 rows among the sequence's new
+    // tokens, part (0: all pages of keys the rows see; 1, 2: the earlier and the later half), then the sequence's
+    // first row in the step, its first new position, its new tokens, its slot, and for a halved tile its number
+    // among the halved tiles
+    const int4 *work;
     PagedCache cache;
+    float *partial_o;   // [halved tiles][heads][32 groups of 4 columns][128 rows][4]: of the half that was through first
+    float *partial_ml;  // [halved tiles][heads][128 rows][2]: its reference (in units of log2) and sum
+    int *tickets;       // [halved tiles][heads][2]: who is through; the partial result is there. Zero before and after
     int *status;
 };
 
@@ -112,8 +124,13 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __
 #endif
     // Before pdl_wait(): what kernels further back than the one just before this wrote (the step's index arrays,
     // the page table), and the CTA's own set-up. The loads that do not depend on one another go out together.
-    const int seq = p.tiles[2 * blockIdx.x], row0 = p.tiles[2 * blockIdx.x + 1], h = blockIdx.y;
-    if (seq < 0) return;  // padding of the work list (a captured step has a fixed number of tiles)
+    const int h = blockIdx.x % p.n_heads, entry = blockIdx.x / p.n_heads;  // all heads of an entry, then the next entry
+    const int4 w0 = p.work[2 * entry], w1 = p.work[2 * entry + 1];
+    const int seq = w0.x, row0 = w0.y, part = w0.z;
+    if (seq < 0) return;  // padding of the work list (a captured step has a fixed length)
+    const bool split = part != 0;
+    const int rank = split ? part - 1 : 0;
+    const long long pair = (long long)w1.w * p.n_heads + h;  // of a halved tile: which partial results and ticket are its
     // an earlier CTA gave up on a wait: do not queue up behind it (one thread looks, so that all decide alike)
     if (threadIdx.x == 0) {
         *(volatile int *)swap = *(volatile int *)(p.status + 3);
@@ -127,17 +144,31 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __
         tc::tma_prefetch_map(&q_map), tc::tma_prefetch_map(&k_map), tc::tma_prefetch_map(&v_map);
     }
     const int kvh = h / (p.n_heads / p.n_kv_heads);
-    const int start = p.seq_start[seq], pos0 = p.seq_pos0[seq], n_new = p.seq_len_after[seq] - pos0;
-    const int slot = p.seq_slot[seq];
+    const int start = w0.w, pos0 = w1.x, n_new = w1.y, slot = w1.z;
     const int last_row = min(row0 + TQ - 1, n_new - 1);
-    const int n_steps = (pos0 + last_row) / TK + 1;  // pages of keys the tile's last row sees
+    const int all_steps = (pos0 + last_row) / TK + 1;  // pages of keys the tile's last row sees
+    // this CTA's pages: of a pair that shares a tile the first takes the earlier half, the second the later one
+    const int cut = split ? (all_steps + 1) / 2 : all_steps;
+    const int first = rank ? cut : 0, my_steps = rank ? all_steps - cut : cut;
+    // the pool rows of the first 32 of them are looked up now, under the set-up
+    int y_first = 0;
+    if (warp == 0 && lane < my_steps) y_first = (cache_page(p.cache, slot, (first + lane) * TK) * p.n_kv_heads + kvh) * TK;
     __syncthreads();
-    if (*(volatile int *)swap) return;  // swap is first written for its own purpose after the next barrier
+    // A CTA that finds the flag set does none of its steps but still takes its ticket if its tile is halved.
+    // swap is first written for its own purpose after the next barrier.
+    const bool quit = *(volatile int *)swap != 0;
+    const int n_steps = quit ? 0 : my_steps;
     if (warp == 1) tc::tmem_alloc(tmem_holder, 256);
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = *tmem_holder, tmem_o = tmem + 128;
+    // what a softmax thread (warps 2-9) keeps for the end; the other warps leave these as they are
+    const int quarter = warp & 3, r = quarter * 32 + lane;  // its query row within the tile
+    const int half = warp >= 2 ? (warp - 2) >> 2 : 0;          // which 32 of a page's 64 keys, and which 64 columns of O
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    float m = -INFINITY, l = 0.0f;  // the reference of the row's exponentials; their sum (this thread's keys; at the end the row's)
+    bool ok = true;
 
     if (warp == 0) {
         // Keys and values have rings of their own: a stage of keys is free once the first product of its
@@ -147,7 +178,9 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __
         int k_issued = 0, v_issued = 0;
         bool go = true;
         for (int base = 0; base < n_steps && go; base += 32) {
-            const int y_lane = base + lane < n_steps ? (cache_page(p.cache, slot, (base + lane) * TK) * p.n_kv_heads + kvh) * TK : 0;
+            const int y_lane = base == 0              ? y_first
+                               : base + lane < n_steps ? (cache_page(p.cache, slot, (first + base + lane) * TK) * p.n_kv_heads + kvh) * TK
+                                                       : 0;
             if (base == 0) {
                 pdl_wait();  // q, and the keys and values of this step's tokens, come from the kernel just before
                 if (lane == 0) {
@@ -193,10 +226,10 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __
         if (lane == 0) {
             constexpr uint32_t idesc_s = tc::idesc_bf16_f32(TQ, TK), idesc_o = idesc_b_mn(TQ, HD);
             const uint32_t qa = tc::smem_addr(q_s);
-            bool ok = tc::mbar_wait(q_full, 0);
+            bool ok = n_steps == 0 || tc::mbar_wait(q_full, 0);
             if (!ok) atomicOr(p.status + 3, 4);
-            // step j: S(j) = Q K(j)^T, then O += P(j-1) V(j-1); one more turn for the last second product
-            for (int j = 0; j <= n_steps && ok; j++) {
+            // step j (of this CTA's): S(j) = Q K(j)^T, then O += P(j-1) V(j-1); one more turn for the last second product
+            for (int j = 0; j <= n_steps && ok && n_steps > 0; j++) {
                 if (j < n_steps) {
                     const int s = j % KV_STAGES, b = j & 1;
                     ok = ok && tc::mbar_wait(&k_full[s], (j / KV_STAGES) & 1);
@@ -237,12 +270,8 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __
         }
     } else {
         pdl_wait();  // before anything is written to global memory
-        const int quarter = warp & 3, r = quarter * 32 + lane;   // this thread's query row within the tile
-        const int half = (warp - 2) >> 2, col0 = half * (TK / 2);  // and its 32 of a page's 64 keys
+        const int col0 = half * (TK / 2);
         const int qpos = pos0 + row0 + r;
-        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        float m = -INFINITY, l = 0.0f;  // l: the sum over this thread's keys only
-        bool ok = true;
         const float GONE = __int_as_float(0x7fc00000);  // what a warp that has given up leaves for its partner
         for (int j = 0; j < n_steps; j++) {
             const int b = j & 1;
@@ -258,11 +287,12 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __
 #pragma unroll
                 for (int c0 = 0; c0 < TK / 2; c0 += 16) tc::tmem_ld16(tmem + lane_base + b * TK + col0 + c0, (uint32_t *)(s + c0));
                 tc::tmem_ld_wait();
-                const bool edge = j * TK + TK - 1 > pos0 + row0;  // some key of this page lies after some row of the tile
+                const int key0 = (first + j) * TK;  // the page's first key
+                const bool edge = key0 + TK - 1 > pos0 + row0;  // some key of this page lies after some row of the tile
                 if (edge) {
 #pragma unroll
                     for (int c = 0; c < TK / 2; c++)
-                        if (j * TK + col0 + c > qpos) s[c] = -INFINITY;
+                        if (key0 + col0 + c > qpos) s[c] = -INFINITY;
                 }
                 // two runs of maxima instead of one of 32 dependent instructions
                 float mx2 = -INFINITY;
@@ -331,8 +361,8 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __
             tc::fence_before_sync();
             tc::mbar_arrive(&p_full[b]);
         }
-        // the last second product, then this row of O / l goes out
-        if (ok && !tc::mbar_wait(o_step, (n_steps - 1) & 1)) {
+        // the last second product of this CTA's pages
+        if (ok && n_steps > 0 && !tc::mbar_wait(o_step, (n_steps - 1) & 1)) {
             atomicOr(p.status + 3, 256);
             ok = false;
         }
@@ -343,24 +373,100 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __
         sums[half * TQ + r] = l;
         pair_sync(quarter);
         l += sums[(half ^ 1) * TQ + r];
+    }
+    // A halved tile: the CTA that is through first (it takes ticket 0) leaves O (column groups of four, so that
+    // the 32 rows of a warp lie side by side), reference and sum in scratch memory and raises a flag; the other
+    // one waits for the flag, adds the two, always in the same order, and stores the rows.
+    float w_own = 1.0f, w_other = 0.0f, l_all = l;
+    const float *other_o = nullptr;
+    bool store = !split;
+    if (split) {
+        __syncthreads();
+        if (threadIdx.x == 0) *(volatile int *)swap = atomicAdd(p.tickets + 2 * pair, 1);
+        __syncthreads();
+        store = *(volatile int *)swap == 1;
+        if (!store) {
+            if (warp >= 2) {
+                tc::fence_after_sync();
+                float *mine_o = p.partial_o + pair * (TQ * HD);
+                if (half == 0) *(float2 *)(p.partial_ml + (pair * TQ + r) * 2) = make_float2(n_steps > 0 ? m : -INFINITY, l);
+#pragma unroll
+                for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+                    uint32_t v[32];
+                    tc::tmem_ld16(tmem_o + lane_base + half * (HD / 2) + c0, v);
+                    tc::tmem_ld16(tmem_o + lane_base + half * (HD / 2) + c0 + 16, v + 16);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int q = 0; q < 8; q++)
+                        *(uint4 *)(mine_o + (((half * (HD / 2) + c0) / 4 + q) * TQ + r) * 4) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                }
+                __threadfence();
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) atomicExch(p.tickets + 2 * pair + 1, 1);  // the partial result is there
+        } else {
+            // the other CTA has its ticket, so it is running: its flag comes within microseconds, or something is broken
+            if (threadIdx.x == 0) {
+                const uint64_t t0 = tc::global_ns();
+                int seen = 0;
+                while (!(seen = atomicAdd(p.tickets + 2 * pair + 1, 0)) && tc::global_ns() - t0 < TC_WAIT_NS) __nanosleep(100);
+                if (!seen) atomicOr(p.status + 3, 512), *failed = 1;
+                p.tickets[2 * pair] = 0, p.tickets[2 * pair + 1] = 0;  // as they were, for the next launch
+                *(volatile int *)swap = seen;
+            }
+            __syncthreads();
+            if (!*(volatile int *)swap) ok = false;
+            __threadfence();
+            if (warp >= 2) {
+                const float2 ml = __ldcg((const float2 *)(p.partial_ml + (pair * TQ + r) * 2));
+                const float own_m = n_steps > 0 ? m : -INFINITY, top = fmaxf(own_m, ml.x);  // one of the two has had pages
+                w_own = own_m == -INFINITY ? 0.0f : exp2f(own_m - top), w_other = ml.x == -INFINITY ? 0.0f : exp2f(ml.x - top);
+                // the earlier half's share first, whoever adds them: the sum does not depend on who came second
+                l_all = rank == 0 ? fmaf(w_other, ml.y, l * w_own) : fmaf(w_own, l, ml.y * w_other);
+                other_o = p.partial_o + pair * (TQ * HD);
+            }
+        }
+    }
+    if (store && warp >= 2) {
+        tc::fence_after_sync();
         // tcgen05.ld is a whole-warp instruction: every lane reads its row, only rows of the sequence are stored
-        if (__all_sync(0xffffffffu, ok)) {
+        if (__all_sync(0xffffffffu, ok) && (n_steps > 0 || split)) {
             const bool mine = row0 + r < n_new;
-            const float inv = 1.0f / l;
+            const float inv = 1.0f / l_all;
             __nv_bfloat16 *dst = p.out + ((long long)(start + row0 + r) * p.n_heads + h) * HD + half * (HD / 2);
-#pragma unroll 1
-            for (int c0 = 0; c0 < HD / 2; c0 += 16) {
-                uint32_t v[16], hpk[8];
+#pragma unroll
+            for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+                uint32_t v[32], hpk[16];
+                float o[32];
+                float4 t[8];
+                if (other_o) {  // (under the loads from tensor memory)
+#pragma unroll
+                    for (int q = 0; q < 8; q++)
+                        t[q] = w_other != 0.0f ? __ldcg((const float4 *)(other_o + (((half * (HD / 2) + c0) / 4 + q) * TQ + r) * 4))
+                                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
                 tc::tmem_ld16(tmem_o + lane_base + half * (HD / 2) + c0, v);
+                tc::tmem_ld16(tmem_o + lane_base + half * (HD / 2) + c0 + 16, v + 16);
                 tc::tmem_ld_wait();
 #pragma unroll
-                for (int e2 = 0; e2 < 8; e2++) {
-                    __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[2 * e2]) * inv, __uint_as_float(v[2 * e2 + 1]) * inv);
-                    hpk[e2] = *(uint32_t *)&t;
+                for (int e = 0; e < 32; e++) o[e] = w_own == 0.0f ? 0.0f : __uint_as_float(v[e]);  // (no pages: nothing was written there)
+                if (other_o) {
+#pragma unroll
+                    for (int q = 0; q < 8; q++) {
+                        const float th[4] = {t[q].x, t[q].y, t[q].z, t[q].w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++)
+                            o[4 * q + e] = rank == 0 ? fmaf(w_other, th[e], o[4 * q + e] * w_own) : fmaf(w_own, o[4 * q + e], th[e] * w_other);
+                    }
+                }
+#pragma unroll
+                for (int e2 = 0; e2 < 16; e2++) {
+                    __nv_bfloat162 tt = __floats2bfloat162_rn(o[2 * e2] * inv, o[2 * e2 + 1] * inv);
+                    hpk[e2] = *(uint32_t *)&tt;
                 }
                 if (mine) {
-                    *(uint4 *)(dst + c0) = make_uint4(hpk[0], hpk[1], hpk[2], hpk[3]);
-                    *(uint4 *)(dst + c0 + 8) = make_uint4(hpk[4], hpk[5], hpk[6], hpk[7]);
+#pragma unroll
+                    for (int q = 0; q < 4; q++) *(uint4 *)(dst + c0 + 8 * q) = make_uint4(hpk[4 * q], hpk[4 * q + 1], hpk[4 * q + 2], hpk[4 * q + 3]);
                 }
             }
         }
@@ -383,14 +489,21 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __
 }
 
 // qkv: the step's rows [n_rows, row_width] (q columns first); out [n_rows, n_heads * 128].
-// tiles: int32 [n_tiles, 2] on the device (sequence, first of 128 rows). No window. status word 3 is set if a wait ran out.
+// work: int32 [n_work, 8] on the device, 16-byte aligned: what each CTA does (see AttnTc), for all heads. A halved
+// tile has two entries and a number below max_halved. No window.
+// scratch: float32 [abk_attention_prefill_tc_scratch_floats(max_halved, n_heads)]; tickets: int32 [2 * max_halved *
+// n_heads], zero before and after. status word 3 is set if a wait ran out.
+extern "C" long long abk_attention_prefill_tc_scratch_floats(int max_halved, int n_heads) {
+    return (long long)max_halved * n_heads * (TQ * HD + TQ * 2);
+}
 extern "C" int abk_attention_prefill_tc(const void *qkv, long long row_width, int n_rows, void *out, int n_heads,
-                                        int n_kv_heads, int head_dim, float scale, const int *tiles, int n_tiles,
-                                        const int *seq_start, const int *seq_pos0, const int *seq_len_after,
-                                        const int *seq_slot, const void *k_pool, const void *v_pool, long long pool_rows,
+                                        int n_kv_heads, int head_dim, float scale, const int *work, int n_work,
+                                        int max_halved, float *scratch, int *tickets, const void *k_pool, const void *v_pool, long long pool_rows,
                                         const int *page_table, int table_width, int tokens_per_page, int *status,
                                         void *stream) {
-    if (n_tiles <= 0) return 0;
+    if (n_work <= 0) return 0;
+    if ((uintptr_t)work % 16 || (uintptr_t)scratch % 16) ABK_REFUSE("attention_prefill_tc: the work list and the scratch memory must be 16-byte aligned");
+    if ((long long)n_work * n_heads > 0x7fffffffLL) ABK_REFUSE("attention_prefill_tc: %d entries for %d heads exceed a grid", n_work, n_heads);
     if (head_dim != HD) ABK_REFUSE("attention_prefill_tc: head_dim %d is not %d", head_dim, HD);
     if (tokens_per_page != TK) ABK_REFUSE("attention_prefill_tc: pages of %d tokens, not %d", tokens_per_page, TK);
     if (n_kv_heads < 1 || n_heads % n_kv_heads || n_heads > 65535) ABK_REFUSE("attention_prefill_tc: %d heads, %d kv heads", n_heads, n_kv_heads);
@@ -402,8 +515,8 @@ extern "C" int abk_attention_prefill_tc(const void *qkv, long long row_width, in
     if (rc) return rc;
     AttnTc p;
     p.out = (__nv_bfloat16 *)out, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
-    p.scale_log2 = scale * 1.4426950408889634f, p.tiles = tiles, p.seq_start = seq_start, p.seq_pos0 = seq_pos0;
-    p.seq_len_after = seq_len_after, p.seq_slot = seq_slot, p.status = status;
+    p.scale_log2 = scale * 1.4426950408889634f, p.work = (const int4 *)work, p.status = status;
+    p.partial_o = scratch, p.partial_ml = scratch + (long long)max_halved * n_heads * (TQ * HD), p.tickets = tickets;
     p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = 0;
     p.cache.tokens_per_page = tokens_per_page;
     const int smem = Q_BYTES + 2 * KV_STAGES * KV_BYTES + P_BYTES + 1024;  // 113 KB: two CTAs to an SM, to the byte
@@ -413,6 +526,7 @@ extern "C" int abk_attention_prefill_tc(const void *qkv, long long row_width, in
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    abk_launch(attn_prefill_tc_kernel, dim3(n_tiles, n_heads), dim3(FA_THREADS), smem, (cudaStream_t)stream, qm, km, vm, p);
+    abk_launch(attn_prefill_tc_kernel, dim3((unsigned)(n_work * n_heads)), dim3(FA_THREADS), smem, (cudaStream_t)stream, qm, km,
+               vm, p);
     return ABK_LAUNCH_RESULT();
 }

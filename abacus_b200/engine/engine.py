@@ -125,7 +125,8 @@ class Engine:
         if b is None or n_rows > b.cap_rows or n_seqs > b.cap_seqs or n_logits > b.cap_logits:
             grow = lambda n, least: max(least, 1 << max(0, int(n) - 1).bit_length())
             b = StepBatch(grow(max(n_rows, b.cap_rows if b else 0), 256), grow(max(n_seqs, b.cap_seqs if b else 0), 16),
-                          grow(max(n_logits, b.cap_logits if b else 0), 64), self.model.ctx.device)
+                          grow(max(n_logits, b.cap_logits if b else 0), 64), self.model.ctx.device,
+                          attention_heads=self.model.attention_heads)
             self._step_batch = b
         return b
 

@@ -37,7 +37,8 @@ class DecodeGraph:
     def __init__(self, engine, rows, position_bound, seqs=None, logit_rows=None):
         self.engine, self.rows, self.position_bound = engine, rows, position_bound
         device = engine.model.ctx.device
-        self.batch = StepBatch(rows, rows if seqs is None else seqs, rows if logit_rows is None else logit_rows, device)
+        self.batch = StepBatch(rows, rows if seqs is None else seqs, rows if logit_rows is None else logit_rows, device,
+                               attention_heads=engine.model.attention_heads)
         self.batch.position_bound = position_bound
         self.graph = None
         self.generation = -1

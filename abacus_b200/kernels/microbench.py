@@ -135,7 +135,7 @@ def _attention_setup(batch, context, heads, kv_heads, head_dim, new_tokens):
         cache.reserve(slot, context)
         seqs.append(Sequence(slot, [0] * new_tokens, context - new_tokens, []))
     rows = batch * new_tokens
-    b = StepBatch(rows, batch, 0, "cuda").fill(seqs)
+    b = StepBatch(rows, batch, 0, "cuda", attention_heads=heads).fill(seqs)
     qkv = torch.randn(rows, (heads + 2 * kv_heads) * head_dim, device="cuda").to(torch.bfloat16)
     out = torch.empty(rows, heads * head_dim, dtype=torch.bfloat16, device="cuda")
     return cache, kv, b, qkv, out

@@ -267,11 +267,15 @@ def attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cac
     pool_rows = cache.k.shape[0] * cache.k.shape[1] * cache.k.shape[2]
     if head_dim == 128 and not PREFILL_ON_MMA:  # tcgen05: tiles of 128 query rows, scores and output in tensor memory
         lib = load_module("attention_tc")
-        tiles = batch.query_tiles(128)
+        work = batch.work  # what each CTA does: whole tiles, long tiles twice (engine/batch.py)
+        sc = _Scratch.of(qkv.device)
+        room = sc.attention_halves_pairs // n_heads
+        if batch.n_halved > room:
+            raise KernelRefused(f"attention_prefill_tc: the step halves {batch.n_halved} tiles, its scratch memory holds "
+                                f"{room} for {n_heads} heads (the StepBatch was made for {batch.attention_heads})")
         _check(lib, lib.abk_attention_prefill_tc(
-            _p(qkv), _ll(row), _i(n), _p(out), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _p(tiles),
-            _i(tiles.shape[0]), _p(batch.seq_start), _p(batch.seq_pos0), _p(batch.seq_len_after), _p(batch.seq_slot),
-            _p(cache.k), _p(cache.v), _ll(pool_rows), _p(cache.page_table), _i(cache.table_width),
+            _p(qkv), _ll(row), _i(n), _p(out), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _p(work),
+            _i(work.shape[0]), _i(room), _p(sc.attention_halves), _p(sc.attention_halves_tickets), _p(cache.k), _p(cache.v), _ll(pool_rows), _p(cache.page_table), _i(cache.table_width),
             _i(cache.tokens_per_page), _p(kernel_status(qkv.device)), _stream()), "attention_prefill_tc")
         return
     tiles = batch.query_tiles(64)
@@ -377,6 +381,22 @@ class _Scratch:
     @property
     def argmax_tickets(self):
         return self._lazy("argmax_tickets", lambda: torch.zeros(self.argmax_rows, dtype=torch.int32, device=self.device))
+
+    attention_halves_pairs = 384  # (tile, head) pairs the prefill attention may halve in one launch (engine/batch.py)
+
+    @property
+    def attention_halves(self):
+        def make():
+            lib = load_module("attention_tc")
+            lib.abk_attention_prefill_tc_scratch_floats.restype = ctypes.c_longlong
+            floats = lib.abk_attention_prefill_tc_scratch_floats(_i(self.attention_halves_pairs), _i(1))
+            return torch.empty(floats, dtype=torch.float32, device=self.device)
+        return self._lazy("attention_halves", make)
+
+    @property
+    def attention_halves_tickets(self):
+        return self._lazy("attention_halves_tickets",
+                          lambda: torch.zeros(2 * self.attention_halves_pairs, dtype=torch.int32, device=self.device))
 
     @property
     def attention_tickets(self):

@@ -65,6 +65,8 @@ class Model:
                                  "which must be an earlier entry with a cache of its own")
         self.ws = Workspace(self.ctx.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.ctx.device)
+        # a hint for whoever shares out attention's work among CTAs: the most heads any mixer runs per token
+        self.attention_heads = max([getattr(getattr(b.mixer, "spec", None), "n_heads", 1) for b in self.blocks] + [1])
 
     # what the cache must hold, entry by entry
     def cache_needs(self):

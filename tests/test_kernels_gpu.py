@@ -160,7 +160,7 @@ class Harness:
             ss.append(Sequence(slot, [0] * n, self.cache.length[slot], []))
             self.cache.reserve(slot, self.cache.length[slot] + n)
         rows = sum(n for _, n in seqs)
-        batch = StepBatch(rows + 3, len(seqs) + 1, 0, "cuda").fill(ss)  # three padding rows at the end
+        batch = self.last_batch = StepBatch(rows + 3, len(seqs) + 1, 0, "cuda").fill(ss)  # three padding rows at the end
         pad = np.full((3, qkv.shape[1]), 7.0, dtype=np.float32)
         q = dev(np.concatenate([qkv, pad]), self.dtype)
         kv = self.cache.views[0].kv
@@ -416,6 +416,42 @@ def test_prefill_attention_on_the_tensor_cores(ops, hq, hkv, hd):
         got = got1[at:at + m] if i != 4 else np.concatenate([got1[at:at + m], got2])
         at += m
         np.testing.assert_allclose(got, want, rtol=2 ** -6, atol=2 ** -6, err_msg=f"prompt {i} of length {n}")
+    assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
+
+
+def test_prefill_attention_halves_long_tiles(ops):
+    """Tiles that see eight pages of keys or more stand twice in the kernel's work list, each CTA with half of
+    the pages; the one that is through first leaves its partial result for the other. A prompt of 700 tokens and
+    one given as 500 and then 300 (its second part's tiles see 9 to 13 pages): against plain attention, twice
+    with the same bits whoever came second, and the tickets back at zero."""
+    from abacus_b200.kernels.ops import _Scratch
+    rng = np.random.default_rng(77)
+    hq, hkv, hd = 4, 2, 128
+    width, scale = (hq + 2 * hkv) * hd, 1.0 / np.sqrt(hd)
+    none = (None, None, 0.0, None, None, 0, False, scale)
+    runs = []
+    for run in range(2):
+        h = Harness(hq, hkv, hd, torch.bfloat16, None, max_tokens=64 * 40)
+        data = [bf(np.random.default_rng(78 + i).standard_normal((n, width)) * 1.5) for i, n in enumerate((700, 800, 200))]
+        slots = [h.cache.open_slot() for _ in data]
+        first = [data[0], data[1][:500], data[2]]
+        _, got1 = h.step(ops, [(s, len(d)) for s, d in zip(slots, first)], np.concatenate(first), *none, general=False)
+        assert h.last_batch.n_halved == 4  # the tiles from row 384 on of the prompts of 700 and of 500 tokens
+        _, got2 = h.step(ops, [(slots[1], 300)], data[1][500:], *none, general=False)
+        assert h.last_batch.n_halved == 3
+        got = [got1[:700], np.concatenate([got1[700:1200], got2]), got1[1200:]]
+        runs.append(got)
+        if run == 0:
+            for i, (d, g) in enumerate(zip(data, got)):
+                n = len(d)
+                q = d[:, :hq * hd].reshape(n, hq, hd)
+                k = d[:, hq * hd:(hq + hkv) * hd].reshape(n, hkv, hd)
+                v = d[:, (hq + hkv) * hd:].reshape(n, hkv, hd)
+                np.testing.assert_allclose(g, plain.attention(q, k, v).reshape(n, hq * hd), rtol=2 ** -6, atol=2 ** -6,
+                                           err_msg=f"prompt {i}")
+    for a, b in zip(*runs):
+        np.testing.assert_array_equal(a, b)
+    assert int(_Scratch.of(torch.device("cuda", 0)).attention_halves_tickets.abs().sum()) == 0
     assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
 
 
