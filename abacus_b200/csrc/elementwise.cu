@@ -277,83 +277,107 @@ template <typename T> __global__ void qkv_prep_kernel(QkvPrep p) {
 // The same for bfloat16 heads of 64 * EPH elements that are rotated whole in half pairing (or not at
 // all): each lane owns EPH consecutive elements of the first half and their partners in the second,
 // read and written as one vector each, with no shared-memory staging.
-template <int N> struct __align__(2 * N) Bf16Pack { __nv_bfloat16 v[N]; };
-#define FAST_WARPS 8
-
-#define FAST_HEADS 4  // heads a warp has in flight at a time
-template <int EPH> __global__ void __launch_bounds__(FAST_WARPS * 32) qkv_prep_fast_kernel(QkvPrep p) {
-    constexpr int HD = 64 * EPH, HALF = 32 * EPH;
-    typedef Bf16Pack<EPH> Pack;
-    // A CTA takes one token; its warps share the token's heads (q, then k, then v), FAST_HEADS at a time so
-    // that their loads are in flight together. Everything but the rows themselves (the step's index arrays,
-    // the page table, the norms' weights, the angles) was written by kernels further back than the one just
-    // before this, and is read before pdl_wait(), once per token instead of once per head.
+#define FAST_WARPS 4
+#define FAST_SLOTS 4  // groups of heads a warp has in flight at a time (its share of a prompt token's 32 heads of 128)
+// bfloat16, head sizes 64, 128 and 256, rotation over the whole head in halves: a lane holds 8 consecutive
+// elements (16 bytes) of a head, so HD / 8 lanes hold a head and a warp 32 * 8 / HD heads at a time. A CTA
+// takes `heads_per_cta` heads of one token (q, then k, then v): all of them for a prompt, where the
+// token's indices, page, weights and angles are then looked up once for 32 heads; a warp's worth for a
+// decode step, so that its few tokens still spread over the SMs. Everything but the rows themselves (the step's index
+// arrays, the page table, the norms' weights, the angles) was written by kernels further back than the one
+// just before this, and is read before pdl_wait().
+template <int HD> __global__ void __launch_bounds__(FAST_WARPS * 32) qkv_prep_fast_kernel(QkvPrep p, int heads_per_cta) {
+    constexpr int LPH = HD / 8, HPW = 32 / LPH;  // lanes per head, heads per warp
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane / LPH, l = lane % LPH;  // which of the warp's heads, and which 8 elements of it
+    const bool upper = l >= LPH / 2;             // the elements that pair with those HD / 2 below them
     const int total_heads = p.n_heads + 2 * p.n_kv_heads;
     const int n_work = p.q_only ? p.n_heads : total_heads;
-    const int seq = p.token_seq[t];
+    const int base = blockIdx.y * heads_per_cta, limit = min(base + heads_per_cta, n_work);
+    // A warp issues its instructions in order and stops at the first whose operand is still on its way, so the
+    // order of the loads is the depth of the chain: sequence and position together; then, with them, the angles,
+    // the slot and the length; then the rows (they need none of these); the page, which needs the slot, last.
+    const int seq = p.token_seq[t], pos = p.token_pos[t];
     if (seq < 0) return;
-    const int pos = p.token_pos[t];
-    float wq_lo[EPH], wq_hi[EPH], wk_lo[EPH], wk_hi[EPH], cs[EPH], sn[EPH];
-#pragma unroll
-    for (int e = 0; e < EPH; e++) {
-        wq_lo[e] = p.q_norm ? p.q_norm[lane * EPH + e] : 1.0f, wq_hi[e] = p.q_norm ? p.q_norm[HALF + lane * EPH + e] : 1.0f;
-        wk_lo[e] = p.k_norm ? p.k_norm[lane * EPH + e] : 1.0f, wk_hi[e] = p.k_norm ? p.k_norm[HALF + lane * EPH + e] : 1.0f;
-        cs[e] = p.cos ? p.cos[(long long)pos * HALF + lane * EPH + e] : 1.0f;
-        sn[e] = p.sin ? p.sin[(long long)pos * HALF + lane * EPH + e] : 0.0f;
+    float cs[8], sn[8];
+    const int at = (upper ? l - LPH / 2 : l) * 8;  // of this lane's elements among the HD / 2 angles
+    float4 c0, c1, s0, s1;
+    if (p.cos) {
+        const float4 *c4 = (const float4 *)(p.cos + (long long)pos * (HD / 2) + at), *s4 = (const float4 *)(p.sin + (long long)pos * (HD / 2) + at);
+        c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
     }
-    long long kept_at = -1;  // where the token's keys and values go in the pools (kv head 0), if they are kept
-    if (!p.q_only && p.k_pool &&
-        !(p.cache.ring_pages > 0 && pos + p.cache.ring_pages * p.cache.tokens_per_page <= p.seq_len_after[seq] - 1))
-        kept_at = cache_offset(p.cache, cache_page(p.cache, p.seq_slot[seq], pos), 0, p.n_kv_heads, pos, HD);
-    __nv_bfloat16 *row0 = (__nv_bfloat16 *)p.qkv + (long long)t * total_heads * HD + lane * EPH;
+    const bool caching = !p.q_only && p.k_pool;
+    const int slot = caching ? p.seq_slot[seq] : 0, len_after = caching ? p.seq_len_after[seq] : 0;
+    if (p.q_norm) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.q_norm + l * 8));  // read where they are used: few registers,
+    if (p.k_norm) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.k_norm + l * 8));  // so that more warps fit an SM
+    __nv_bfloat16 *row0 = (__nv_bfloat16 *)p.qkv + (long long)t * total_heads * HD + l * 8;
     pdl_wait();
-    for (int h0 = warp; h0 < n_work; h0 += FAST_WARPS * FAST_HEADS) {
-        Pack lo[FAST_HEADS], hi[FAST_HEADS];
+    long long kept_at = -1;  // where the token's keys and values go in the pools (kv head 0), if they are kept
+    bool first_round = true;
+    for (int h0 = base + warp * HPW + sub; h0 - sub < limit; h0 += FAST_WARPS * HPW * FAST_SLOTS) {
+        uint4 raw[FAST_SLOTS];
 #pragma unroll
-        for (int u = 0; u < FAST_HEADS; u++) {
-            const int head = h0 + u * FAST_WARPS;
-            if (head < n_work) lo[u] = *(const Pack *)(row0 + (long long)head * HD), hi[u] = *(const Pack *)(row0 + (long long)head * HD + HALF);
+        for (int u = 0; u < FAST_SLOTS; u++) {
+            const int head = h0 + u * FAST_WARPS * HPW;
+            raw[u] = head < limit ? *(const uint4 *)(row0 + (long long)head * HD) : make_uint4(0, 0, 0, 0);
+        }
+        if (first_round) {  // (after the rows are on their way)
+            first_round = false;
+            if (caching && !(p.cache.ring_pages > 0 && pos + p.cache.ring_pages * p.cache.tokens_per_page <= len_after - 1))
+                kept_at = cache_offset(p.cache, cache_page(p.cache, slot, pos), 0, p.n_kv_heads, pos, HD);
+            if (p.cos) {
+                cs[0] = c0.x, cs[1] = c0.y, cs[2] = c0.z, cs[3] = c0.w, cs[4] = c1.x, cs[5] = c1.y, cs[6] = c1.z, cs[7] = c1.w;
+                sn[0] = s0.x, sn[1] = s0.y, sn[2] = s0.z, sn[3] = s0.w, sn[4] = s1.x, sn[5] = s1.y, sn[6] = s1.z, sn[7] = s1.w;
+            }
         }
 #pragma unroll
-        for (int u = 0; u < FAST_HEADS; u++) {
-            const int head = h0 + u * FAST_WARPS;
-            if (head >= n_work) break;
+        for (int u = 0; u < FAST_SLOTS; u++) {
+            const int head = h0 + u * FAST_WARPS * HPW;
+            if (head - sub >= limit) break;  // the whole warp is past the end (the shuffles below are for whole warps)
+            const bool live = head < limit;
             const bool is_q = head < p.n_heads, is_k = !is_q && head < p.n_heads + p.n_kv_heads;
             const int kv_head = is_q ? 0 : is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
+            const uint32_t in[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float2 f = __bfloat1622float2(*(const __nv_bfloat162 *)&in[e]);
+                v[2 * e] = f.x, v[2 * e + 1] = f.y;
+            }
+            float ss = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; e++) ss += v[e] * v[e];
+#pragma unroll
+            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);  // over the head's lanes
+            const float *w = is_q ? p.q_norm : p.k_norm;
+            if ((is_q || is_k) && w) {
+                const float scale = 1.0f / sqrtf(ss / (float)HD + p.eps);
+                const float4 w0 = __ldg((const float4 *)(w + l * 8)), w1 = __ldg((const float4 *)(w + l * 8 + 4));
+                const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] = wv[e] * (v[e] * scale);
+            }
+            // the element HD / 2 above or below each of this lane's, from the lane that holds it
+            float other[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) other[e] = __shfl_xor_sync(0xffffffffu, v[e], LPH / 2);
+            uint32_t outw[4] = {in[0], in[1], in[2], in[3]};
             if (is_q || is_k) {
-                float a[EPH], b[EPH], ss = 0.0f;
-#pragma unroll
-                for (int e = 0; e < EPH; e++) {
-                    a[e] = __bfloat162float(lo[u].v[e]), b[e] = __bfloat162float(hi[u].v[e]);
-                    ss += a[e] * a[e] + b[e] * b[e];
-                }
-                if (is_q ? p.q_norm != nullptr : p.k_norm != nullptr) {
-                    ss = warp_sum(ss);
-                    const float scale = 1.0f / sqrtf(ss / (float)HD + p.eps);
-#pragma unroll
-                    for (int e = 0; e < EPH; e++) {
-                        a[e] = (is_q ? wq_lo[e] : wk_lo[e]) * (a[e] * scale);
-                        b[e] = (is_q ? wq_hi[e] : wk_hi[e]) * (b[e] * scale);
-                    }
-                }
                 if (p.cos) {
 #pragma unroll
-                    for (int e = 0; e < EPH; e++) {
-                        float x = a[e], y = b[e];
-                        a[e] = x * cs[e] - y * sn[e];
-                        b[e] = y * cs[e] + x * sn[e];
-                    }
+                    for (int e = 0; e < 8; e++) v[e] = upper ? v[e] * cs[e] + other[e] * sn[e] : v[e] * cs[e] - other[e] * sn[e];
                 }
 #pragma unroll
-                for (int e = 0; e < EPH; e++) lo[u].v[e] = __float2bfloat16_rn(a[e]), hi[u].v[e] = __float2bfloat16_rn(b[e]);
-                __nv_bfloat16 *row = row0 + (long long)head * HD;
-                *(Pack *)row = lo[u], *(Pack *)(row + HALF) = hi[u];
+                for (int e = 0; e < 4; e++) {
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                    outw[e] = *(uint32_t *)&h2;
+                }
+                if (live) *(uint4 *)(row0 + (long long)head * HD) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
             }
-            if (!is_q && kept_at >= 0) {
+            if (live && !is_q && kept_at >= 0) {
                 __nv_bfloat16 *dst = (__nv_bfloat16 *)(is_k ? p.k_pool : p.v_pool) + kept_at +
-                                     (long long)kv_head * p.cache.tokens_per_page * HD + lane * EPH;
-                *(Pack *)dst = lo[u], *(Pack *)(dst + HALF) = hi[u];
+                                     (long long)kv_head * p.cache.tokens_per_page * HD + l * 8;
+                *(uint4 *)dst = make_uint4(outw[0], outw[1], outw[2], outw[3]);
             }
         }
     }
@@ -380,11 +404,16 @@ extern "C" int abk_qkv_prep(void *qkv, int dtype, int n_tokens, int n_heads, int
     dim3 grid(n_tokens, (total_heads + PREP_WARPS - 1) / PREP_WARPS);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == ABK_BF16 && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
-        (!cos || (rotary_dim == head_dim && !interleaved)) && (uintptr_t)qkv % 16 == 0) {
-        dim3 fast((unsigned)n_tokens);
-        if (head_dim == 64) abk_launch(qkv_prep_fast_kernel<1>, fast, dim3(FAST_WARPS * 32), 0, s, p);
-        else if (head_dim == 128) abk_launch(qkv_prep_fast_kernel<2>, fast, dim3(FAST_WARPS * 32), 0, s, p);
-        else abk_launch(qkv_prep_fast_kernel<4>, fast, dim3(FAST_WARPS * 32), 0, s, p);
+        (!cos || (rotary_dim == head_dim && !interleaved)) &&
+        ((uintptr_t)qkv | (uintptr_t)cos | (uintptr_t)sin | (uintptr_t)q_norm | (uintptr_t)k_norm | (uintptr_t)k_pool |
+         (uintptr_t)v_pool) % 16 == 0) {
+        // prompts: a token's heads in one CTA; a decode step of few tokens: one round of its warps' heads to a CTA
+        const int work = q_only ? n_heads : total_heads;
+        const int per_cta = n_tokens >= 64 ? work : FAST_WARPS * (256 / head_dim);
+        dim3 fast((unsigned)n_tokens, (unsigned)((work + per_cta - 1) / per_cta));
+        if (head_dim == 64) abk_launch(qkv_prep_fast_kernel<64>, fast, dim3(FAST_WARPS * 32), 0, s, p, per_cta);
+        else if (head_dim == 128) abk_launch(qkv_prep_fast_kernel<128>, fast, dim3(FAST_WARPS * 32), 0, s, p, per_cta);
+        else abk_launch(qkv_prep_fast_kernel<256>, fast, dim3(FAST_WARPS * 32), 0, s, p, per_cta);
         return ABK_LAUNCH_RESULT();
     }
     if (dtype == ABK_BF16)
