@@ -124,6 +124,16 @@ template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// silu(gate) * up for the bfloat16 path (src/model.c:274-282): the exponential and the reciprocal by the
+// special-function unit (a few units in the last place of float32, far below the bfloat16 the result is
+// stored in). Every bfloat16 kernel uses this one, so a token's activation is the same on every way.
+__device__ __forceinline__ float silu_mul_fast(float gate, float up) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(gate * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return gate * r * up;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

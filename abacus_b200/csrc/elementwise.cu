@@ -139,49 +139,54 @@ extern "C" int abk_add_rmsnorm(float *x, const float *y, const float *w, void *o
 }
 
 // ------------------------------------------------------------------ SwiGLU
-// act[t, j] = silu(gate_up[t, j]) * gate_up[t, inter + j]              (src/model.c:274-282)
+// act[t, j] = silu(gate[t, j]) * up[t, j]                              (src/model.c:274-282)
+// A row of gate_up holds gate and up in turns of `block` columns: gate of features [0, block), up of the same,
+// gate of [block, 2 block), ... With block = inter that is all gates and then all ups (src/model.c:98).
+__device__ __forceinline__ long long gate_column(int j, int block) { return (long long)(j / block) * 2 * block + j % block; }
 template <typename T>
-__global__ void swiglu_kernel(const T *__restrict__ gate_up, T *__restrict__ act, long long total, int inter) {
+__global__ void swiglu_kernel(const T *__restrict__ gate_up, T *__restrict__ act, long long total, int inter, int block) {
     pdl_wait();
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
          e += (long long)gridDim.x * blockDim.x) {
         long long t = e / inter;
         int j = (int)(e - t * inter);
-        float g = to_float(gate_up[t * 2 * inter + j]);
-        float u = to_float(gate_up[t * 2 * inter + inter + j]);
-        act[e] = from_float<T>(g / (1.0f + expf(-g)) * u);
+        float g = to_float(gate_up[t * 2 * inter + gate_column(j, block)]);
+        float u = to_float(gate_up[t * 2 * inter + gate_column(j, block) + block]);
+        act[e] = from_float<T>(sizeof(T) == 2 ? silu_mul_fast(g, u) : g / (1.0f + expf(-g)) * u);
     }
 }
 
-// bfloat16 with inter a multiple of 8: eight elements a thread, read and written as 16-byte vectors.
+// bfloat16 with inter and block multiples of 8: eight elements a thread, read and written as 16-byte vectors.
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16 *__restrict__ gate_up, __nv_bfloat16 *__restrict__ act,
-                                     long long groups, int inter) {
+                                     long long groups, int inter, int block) {
     pdl_wait();
     const int per_row = inter >> 3;
     for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += (long long)gridDim.x * blockDim.x) {
         long long t = g / per_row;
         int j = (int)(g - t * per_row) << 3;
-        uint4 graw = *(const uint4 *)(gate_up + t * 2 * inter + j), uraw = *(const uint4 *)(gate_up + t * 2 * inter + inter + j);
+        const __nv_bfloat16 *gcol = gate_up + t * 2 * inter + gate_column(j, block);
+        uint4 graw = *(const uint4 *)gcol, uraw = *(const uint4 *)(gcol + block);
         const __nv_bfloat162 *gp = (const __nv_bfloat162 *)&graw, *up = (const __nv_bfloat162 *)&uraw;
         uint4 out;
         __nv_bfloat162 *op = (__nv_bfloat162 *)&out;
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             float2 gv = __bfloat1622float2(gp[e]), uv = __bfloat1622float2(up[e]);
-            op[e] = __floats2bfloat162_rn(gv.x / (1.0f + expf(-gv.x)) * uv.x, gv.y / (1.0f + expf(-gv.y)) * uv.y);
+            op[e] = __floats2bfloat162_rn(silu_mul_fast(gv.x, uv.x), silu_mul_fast(gv.y, uv.y));
         }
         *(uint4 *)(act + t * inter + j) = out;
     }
 }
 
-extern "C" int abk_swiglu(const void *gate_up, void *act, int dtype, int n_tokens, int inter, void *stream) {
+extern "C" int abk_swiglu(const void *gate_up, void *act, int dtype, int n_tokens, int inter, int block, void *stream) {
     long long total = (long long)n_tokens * inter;
     if (total <= 0) return 0;
-    if (dtype == ABK_BF16 && inter % 8 == 0 && ((uintptr_t)gate_up | (uintptr_t)act) % 16 == 0) {
+    if (block <= 0 || inter % block) ABK_REFUSE("swiglu: turns of %d columns do not divide %d", block, inter);
+    if (dtype == ABK_BF16 && inter % 8 == 0 && block % 8 == 0 && ((uintptr_t)gate_up | (uintptr_t)act) % 16 == 0) {
         long long groups = total >> 3, want = (groups + 255) / 256;
         int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
         abk_launch(swiglu_bf16x8_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16 *)gate_up,
-                   (__nv_bfloat16 *)act, groups, inter);
+                   (__nv_bfloat16 *)act, groups, inter, block);
         return ABK_LAUNCH_RESULT();
     }
     int threads = 256;
@@ -189,9 +194,9 @@ extern "C" int abk_swiglu(const void *gate_up, void *act, int dtype, int n_token
     if (blocks > 148 * 32) blocks = 148 * 32;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == ABK_BF16)
-        abk_launch(swiglu_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, (const __nv_bfloat16 *)gate_up, (__nv_bfloat16 *)act, total, inter);
+        abk_launch(swiglu_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, (const __nv_bfloat16 *)gate_up, (__nv_bfloat16 *)act, total, inter, block);
     else
-        abk_launch(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, (const float *)gate_up, (float *)act, total, inter);
+        abk_launch(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, (const float *)gate_up, (float *)act, total, inter, block);
     return ABK_LAUNCH_RESULT();
 }
 

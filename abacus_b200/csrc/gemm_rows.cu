@@ -45,8 +45,9 @@ __device__ __forceinline__ uint4 load16(const __nv_bfloat16 *p, bool ok) {
 // NT: tiles of 8 tokens (1, 2, 4 or 8: up to 64 rows; every CTA reads all of x, which stays in the L2).
 // TILE: output features a CTA owns, 16 or 8. With 8 the upper half of the 16-row product is zero and
 // twice as many CTAs share the matrix: for matrices with too few rows to give every SM a tile of 16.
-// GATED: w holds N gate rows and then N up rows (src/model.c:98); a CTA owns 8 outputs, takes their gate
-// rows as the lower and their up rows as the upper half of the product, and stores silu(gate) * up
+// GATED: w holds gate and up rows in turns of `block` rows (gate of features [0, block), up of the same, gate of
+// the next block, ...; block = N: all gates, then all ups, src/model.c:98); a CTA owns 8 outputs, takes their
+// gate rows as the lower and their up rows as the upper half of the product, and stores silu(gate) * up
 // (src/model.c:274-282) instead of the two sums: the feed-forward's first product and its activation in one.
 __device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
@@ -54,13 +55,15 @@ template <int NT, int TILE, bool GATED, typename TO>
 __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bfloat16 *__restrict__ x,
                                                                  const __nv_bfloat16 *__restrict__ w, TO *__restrict__ out,
                                                                  int M, int N, int K, long long ldx, long long ldw,
-                                                                 long long ldo) {
+                                                                 long long ldo, int block) {
     __shared__ float part[ROWS_WARPS][16][8 * NT + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
     const int ranks = (int)tc::cluster_size(), rank = (int)tc::cluster_rank();  // the cluster splits K
     const int n0 = (blockIdx.x / ranks) * TILE;
     const bool row_lo = n0 + r < N, row_hi = GATED ? row_lo : TILE == 16 && n0 + r + 8 < N;
-    const __nv_bfloat16 *w_lo = w + (long long)(n0 + r) * ldw + 8 * c, *w_hi = w_lo + (GATED ? (long long)N : 8) * ldw;
+    // (a turn of gate rows is a multiple of 8 long, so a CTA's 8 outputs lie in one turn)
+    const long long w_row = GATED ? (long long)(n0 / block) * 2 * block + n0 % block + r : n0 + r;
+    const __nv_bfloat16 *w_lo = w + w_row * ldw + 8 * c, *w_hi = w_lo + (GATED ? (long long)block : 8) * ldw;
     const __nv_bfloat16 *x0 = x + (long long)r * ldx + 8 * c;  // token r of tile t is 8 t rows further
     float acc[NT][4];
 #pragma unroll
@@ -151,7 +154,7 @@ __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bflo
                 // gate and up pass through bfloat16, as they do where they are stored between the product
                 // and the activation (larger steps): a token's result is the same on either way
                 sum = __bfloat162float(__float2bfloat16_rn(sum)), up = __bfloat162float(__float2bfloat16_rn(up));
-                sum = sum / (1.0f + expf(-sum)) * up;
+                sum = silu_mul_fast(sum, up);
             }
             out[(long long)token * ldo + n0 + row] = from_float<TO>(sum);
         }
@@ -179,7 +182,7 @@ extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dt
     const __nv_bfloat16 *xb = (const __nv_bfloat16 *)x, *wb = (const __nv_bfloat16 *)w;
 #define ROWS_LAUNCH(NT, TILE, TO)                                                                                     \
     abk_launch_clusters(gemm_rows_kernel<NT, TILE, false, TO>, grid, dim3(ROWS_THREADS), 0, s, ranks, xb, wb, (TO *)out, M, \
-                        N, K, ldx, ldw, ldo)
+                        N, K, ldx, ldw, ldo, 0)
 #define ROWS_BY_M(TO)                                                                     \
     if (M <= 8) { if (narrow) ROWS_LAUNCH(1, 8, TO); else ROWS_LAUNCH(1, 16, TO); }       \
     else if (M <= 16) { if (narrow) ROWS_LAUNCH(2, 8, TO); else ROWS_LAUNCH(2, 16, TO); } \
@@ -191,11 +194,13 @@ extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dt
     return ABK_LAUNCH_RESULT();
 }
 
-// act[M, N] = silu(x . w_gate^T) * (x . w_up^T) where w [2 N, K] holds the gate rows and then the up rows.
-// x, w bfloat16; act bfloat16. M <= 16, K a multiple of 32.
+// act[M, N] = silu(x . w_gate^T) * (x . w_up^T) where w [2 N, K] holds gate and up rows in turns of `block`
+// rows (a multiple of 8 that divides N; N itself: all gates, then all ups).
+// x, w bfloat16; act bfloat16. M <= 64, K a multiple of 32.
 extern "C" int abk_gemm_rows_swiglu(const void *x, const void *w, void *act, int M, int N, int K, long long ldx,
-                                    long long ldw, long long ldo, void *stream) {
+                                    long long ldw, long long ldo, int block, void *stream) {
     if (M <= 0 || N <= 0) return 0;
+    if (block <= 0 || N % block || (block % 8 && block != N)) ABK_REFUSE("gemm_rows_swiglu: turns of %d rows do not fit %d features", block, N);
     if (M > 64) ABK_REFUSE("gemm_rows_swiglu: %d rows are more than 64", M);
     if (K <= 0 || K % 32 || ldx % 8 || ldw % 8) ABK_REFUSE("gemm_rows_swiglu: K = %d must be a multiple of 32 and the pitches of 8", K);
     if (((uintptr_t)x | (uintptr_t)w) & 15) ABK_REFUSE("gemm_rows_swiglu: operands must be 16-byte aligned");
@@ -203,7 +208,7 @@ extern "C" int abk_gemm_rows_swiglu(const void *x, const void *w, void *act, int
     cudaStream_t s = (cudaStream_t)stream;
     const __nv_bfloat16 *xb = (const __nv_bfloat16 *)x, *wb = (const __nv_bfloat16 *)w;
 #define GATED_LAUNCH(NT) \
-    abk_launch(gemm_rows_kernel<NT, 8, true, __nv_bfloat16>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (__nv_bfloat16 *)act, M, N, K, ldx, ldw, ldo)
+    abk_launch(gemm_rows_kernel<NT, 8, true, __nv_bfloat16>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (__nv_bfloat16 *)act, M, N, K, ldx, ldw, ldo, block)
     if (M <= 8) GATED_LAUNCH(1);
     else if (M <= 16) GATED_LAUNCH(2);
     else if (M <= 32) GATED_LAUNCH(4);

@@ -221,7 +221,12 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
 // Tile t is rows (t % m_tiles) * 128 and columns (t / m_tiles) * BN; CTA c takes tiles c, c + grid, ...
 // Warp 0 loads, warp 1 issues the products into accumulator (i & 1) of its i-th tile, warps 2-5 store
 // the accumulator of the tile before. acc_full / acc_empty hand the two accumulators back and forth.
-template <int BN, int STAGES, typename TO>
+// GATED (BN 256, bfloat16 out): the columns of a tile are the gates of 128 features and then their ups (the
+// weight's rows come in such turns of 128), and what is stored is out[p, 128 t + j] = silu(gate) * up, both
+// rounded to bfloat16 first, as they are where they are stored between the product and the activation: the
+// feed-forward's first product and its activation in one (src/model.c:274-282, 307-308). g.Q is then the
+// number of features, half of the product's columns.
+template <int BN, int STAGES, typename TO, bool GATED = false>
 __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p,
                                                                           const __grid_constant__ CUtensorMap map_q,
                                                                           GemmTc g, int m_tiles, int tiles) {
@@ -313,22 +318,45 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_persistent_kernel(const 
                 break;
             }
             tc::fence_after_sync();
+            if constexpr (GATED) {
+                const int f0 = (t / m_tiles) * (BN / 2);  // the tile's first feature
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c0, v);
-                tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c0 + 16, v + 16);
-                tc::tmem_ld_wait();
+                for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+                    uint32_t gv[32], uv[32];
+                    tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c0, gv);
+                    tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c0 + 16, gv + 16);
+                    tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + BN / 2 + c0, uv);
+                    tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + BN / 2 + c0 + 16, uv + 16);
+                    tc::tmem_ld_wait();
 #pragma unroll
-                for (int h = 0; h < 32; h += 16) {
-                    if (g.vec && p < g.P && q0 + c0 + h + 16 <= g.Q) {
-                        store16(out + (long long)p * g.stride_p + q0 + c0 + h, v + h);
-                    } else if (p < g.P) {
+                    for (int j = 0; j < 32; j++) {
+                        const float gate = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gv[j])));
+                        const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(uv[j])));
+                        gv[j] = __float_as_uint(silu_mul_fast(gate, up));
+                    }
+                    if (p < g.P && f0 + c0 + 32 <= g.Q) {
+                        store16(out + (long long)p * g.stride_p + f0 + c0, gv);
+                        store16(out + (long long)p * g.stride_p + f0 + c0 + 16, gv + 16);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c0, v);
+                    tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c0 + 16, v + 16);
+                    tc::tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 16; j++)
-                            if (q0 + c0 + h + j < g.Q)
-                                out[(long long)p * g.stride_p + (long long)(q0 + c0 + h + j) * g.stride_q] =
-                                    from_float<TO>(__uint_as_float(v[h + j]));
+                    for (int h = 0; h < 32; h += 16) {
+                        if (g.vec && p < g.P && q0 + c0 + h + 16 <= g.Q) {
+                            store16(out + (long long)p * g.stride_p + q0 + c0 + h, v + h);
+                        } else if (p < g.P) {
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                if (q0 + c0 + h + j < g.Q)
+                                    out[(long long)p * g.stride_p + (long long)(q0 + c0 + h + j) * g.stride_q] =
+                                        from_float<TO>(__uint_as_float(v[h + j]));
+                        }
                     }
                 }
             }
@@ -434,6 +462,36 @@ static int launch_persistent(const CUtensorMap &mp, const CUtensorMap &mq, const
         configured = true;
     }
     abk_launch(kernel, dim3(tiles < 148 ? tiles : 148), dim3(GEMM_THREADS), (size_t)bytes, s, mp, mq, g, m_tiles, tiles);
+    return ABK_LAUNCH_RESULT();
+}
+
+// act[M, N] = silu(x . gate^T) * (x . up^T), w [2 N, K] holding gate and up rows in turns of 128: the persistent
+// kernel with the activation in its epilogue. Many rows only (more than 256), N a multiple of 128, act bfloat16
+// with 16-byte aligned rows; other shapes are refused (the caller multiplies and activates in two steps).
+extern "C" int abk_gemm_tc_swiglu(const void *x, const void *w, void *act, int M, int N, int K, long long ldx,
+                                  long long ldw, long long ldo, int *status, void *stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M <= 256 || N % 128 || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldo % 8 || (((uintptr_t)x | (uintptr_t)w | (uintptr_t)act) & 15))
+        ABK_REFUSE("gemm_tc_swiglu: %d rows, %d features, K = %d are not what the fused kernel takes", M, N, K);
+    CUtensorMap mx, mw;
+    int rc = tensor_map(x, M, K, ldx, TILE_P, &mx);
+    if (!rc) rc = tensor_map(w, 2LL * N, K, ldw, 256, &mw);
+    if (rc) return rc;
+    GemmTc g;
+    g.out = act, g.P = M, g.Q = N, g.K = K, g.stride_p = ldo, g.stride_q = 1;
+    g.k_blocks = (K + TILE_K - 1) / TILE_K, g.k_blocks_per_split = g.k_blocks, g.splits = 1;
+    g.partials = nullptr, g.tickets = nullptr, g.status = status, g.vec = 1;
+    const int m_tiles = (M + TILE_P - 1) / TILE_P, tiles = m_tiles * (N / 128);
+    auto kernel = gemm_tc_persistent_kernel<256, 4, __nv_bfloat16, true>;
+    static bool configured = false;
+    constexpr int bytes = GemmSmem<256, 4>::BYTES;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    abk_launch(kernel, dim3(tiles < 148 ? tiles : 148), dim3(GEMM_THREADS), (size_t)bytes, (cudaStream_t)stream, mx, mw, g,
+               m_tiles, tiles);
     return ABK_LAUNCH_RESULT();
 }
 

@@ -89,14 +89,17 @@ def add_rmsnorm(x, y, weight, out, eps, rows=None, n_rows=None):
                                     _f(eps), _stream()), "add_rmsnorm")
 
 
-def swiglu(gate_up, act):
-    """act = silu(gate) * up for rows laid out [gate | up] (src/model.c:274-282)."""
+def swiglu(gate_up, act, block=None):
+    """act = silu(gate) * up (src/model.c:274-282). A row of gate_up holds gate and up in turns of `block`
+    columns (gate of features [0, block), up of the same, gate of the next block, ...); by default all gates
+    and then all ups."""
     _need_cuda(gate_up, act)
     lib = load_module("elementwise")
     n, two_i = gate_up.shape
     assert act.shape == (n, two_i // 2) and act.dtype == gate_up.dtype
     assert gate_up.is_contiguous() and act.is_contiguous()
-    _check(lib, lib.abk_swiglu(_p(gate_up), _p(act), _i(_dt(act)), _i(n), _i(two_i // 2), _stream()), "swiglu")
+    _check(lib, lib.abk_swiglu(_p(gate_up), _p(act), _i(_dt(act)), _i(n), _i(two_i // 2), _i(block or two_i // 2),
+                               _stream()), "swiglu")
 
 
 def qkv_prep(qkv, n_heads, n_kv_heads, head_dim, batch, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved,
@@ -192,16 +195,40 @@ def gemm_rows(x, w, out, m=None):
                                   _ll(w.stride(0)), _ll(out.stride(0)), _stream()), "gemm_rows")
 
 
-def gemm_rows_swiglu(x, w_gate_up, act, m=None):
-    """act[:m] = silu(x . gate^T) * (x . up^T) for m <= 16 rows, w_gate_up [2 I, K] holding the gate rows and
-    then the up rows: the feed-forward's first product and its activation in one kernel (src/model.c:307-308)."""
+def gemm_rows_swiglu(x, w_gate_up, act, m=None, block=None):
+    """act[:m] = silu(x . gate^T) * (x . up^T) for m <= 64 rows, w_gate_up [2 I, K] holding gate and up rows in
+    turns of `block` rows (by default all gates, then all ups): the feed-forward's first product and its
+    activation in one kernel (src/model.c:307-308)."""
     _need_cuda(x, w_gate_up, act)
     lib = load_module("gemm_rows")
     m = x.shape[0] if m is None else m
     two_i, k = w_gate_up.shape
     assert x.shape[1] == k and act.shape[1] == two_i // 2 and act.dtype == torch.bfloat16 and act.stride(1) == 1
     _check(lib, lib.abk_gemm_rows_swiglu(_p(x), _p(w_gate_up), _p(act), _i(m), _i(two_i // 2), _i(k), _ll(x.stride(0)),
-                                         _ll(w_gate_up.stride(0)), _ll(act.stride(0)), _stream()), "gemm_rows_swiglu")
+                                         _ll(w_gate_up.stride(0)), _ll(act.stride(0)), _i(block or two_i // 2), _stream()),
+           "gemm_rows_swiglu")
+
+
+def gemm_tc_swiglu_takes(x, w_gate_up, act, m, block):
+    """Whether the tensor-core product with the activation in its epilogue takes this: many rows, gate and up
+    rows in turns of 128."""
+    return (block == 128 and m > 256 and act.dtype == torch.bfloat16 and w_gate_up.shape[0] % 256 == 0
+            and act.stride(0) % 8 == 0 and act.data_ptr() % 16 == 0 and gemm_tc_takes(x, w_gate_up, act))
+
+
+def gemm_tc_swiglu(x, w_gate_up, act, m=None):
+    """act[:m] = silu(x . gate^T) * (x . up^T) on the tcgen05 tensor cores for more than 256 rows, w_gate_up
+    [2 I, K] holding gate and up rows in turns of 128: the activation runs in the product's epilogue, under the
+    next tile's multiplication (src/model.c:307-308)."""
+    _need_cuda(x, w_gate_up, act)
+    lib = load_module("gemm_tc")
+    m = x.shape[0] if m is None else m
+    two_i, k = w_gate_up.shape
+    assert x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and act.dtype == torch.bfloat16
+    assert x.shape[1] == k and act.shape[1] == two_i // 2 and x.stride(1) == 1 and w_gate_up.stride(1) == 1 and act.stride(1) == 1
+    _check(lib, lib.abk_gemm_tc_swiglu(_p(x), _p(w_gate_up), _p(act), _i(m), _i(two_i // 2), _i(k), _ll(x.stride(0)),
+                                       _ll(w_gate_up.stride(0)), _ll(act.stride(0)), _p(_Scratch.of(x.device).status),
+                                       _stream()), "gemm_tc_swiglu")
 
 
 def argmax(logits, out, n_rows=None):

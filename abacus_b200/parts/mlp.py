@@ -1,6 +1,8 @@
 """Gated feed-forward: down(silu(gate(x)) * up(x)) (src/model.c:274-282, 307-309).
 
-gate and up are one stacked matrix, as in src/model.c:98.
+gate and up are one matrix, as in src/model.c:98. In bfloat16, when the inner size allows, its rows come
+in turns of 128 (gate of features 0-127, up of the same, gate of 128-255, ...): a 256-column tile of the
+tensor-core product then holds both halves of 128 features, and the activation runs in its epilogue.
 """
 import torch
 
@@ -22,19 +24,28 @@ class GatedMLP:
         s = self.spec
         return {"gate": (s.inter, s.hidden), "up": (s.inter, s.hidden), "down": (s.hidden, s.inter)}
 
+    TURN = 128  # rows of gate, then of up, where the layout comes in turns
+
     def bind(self, params, ctx):
         self.ctx = ctx
-        self.gate_up = Linear(to_device(torch.cat([params["gate"], params["up"]], dim=0), ctx, ctx.dtype))
+        inter, gate, up = self.spec.inter, params["gate"], params["up"]
+        self.block = self.TURN if ctx.dtype == torch.bfloat16 and inter % self.TURN == 0 else inter
+        turns = inter // self.block
+        stacked = torch.stack([gate.reshape(turns, self.block, -1), up.reshape(turns, self.block, -1)], dim=1)
+        self.gate_up = Linear(to_device(stacked.reshape(2 * inter, -1).contiguous(), ctx, ctx.dtype))
         self.down = Linear(to_device(params["down"], ctx, ctx.dtype))
 
     def forward(self, xn, out, batch, ws):
         n, inter = batch.n_rows, self.spec.inter
         act = ws.get("act", (n, inter), self.ctx.dtype)
-        if n <= ROWS_KERNEL_UP_TO and ops.gemm_rows_takes(xn, self.gate_up.weight, act, n):
-            ops.gemm_rows_swiglu(xn, self.gate_up.weight, act, n)  # a handful of rows: product and activation in one
+        w = self.gate_up.weight
+        if n <= ROWS_KERNEL_UP_TO and ops.gemm_rows_takes(xn, w, act, n):
+            ops.gemm_rows_swiglu(xn, w, act, n, self.block)  # a handful of rows: product and activation in one
+        elif ops.gemm_tc_swiglu_takes(xn, w, act, n, self.block):
+            ops.gemm_tc_swiglu(xn, w, act, n)  # a prompt: the activation in the product's epilogue
         else:
             gate_up = ws.get("gate_up", (n, 2 * inter), self.ctx.dtype)
             self.gate_up.forward(xn, gate_up, n)
-            ops.swiglu(gate_up, act)
+            ops.swiglu(gate_up, act, self.block)
         self.down.forward(act, out, n)
         return out

@@ -74,6 +74,10 @@ def test_swiglu(ops, dtype):
     act = torch.empty(9, 100, dtype=dtype, device="cuda")
     ops.swiglu(dev(gu, dtype), act)
     close(act, plain.swiglu(gu), dtype)
+    # gate and up in turns of 20 columns instead of all gates and then all ups
+    turns = np.concatenate([np.concatenate([gu[:, b:b + 20], gu[:, 100 + b:100 + b + 20]], -1) for b in range(0, 100, 20)], -1)
+    ops.swiglu(dev(turns, dtype), act, block=20)
+    close(act, plain.swiglu(gu), dtype)
 
 
 @pytest.mark.parametrize("m, n, k", [(5, 37, 50), (1, 389, 96), (130, 70, 33), (64, 64, 16), (3, 1, 7)])
@@ -484,3 +488,28 @@ def test_gemm_rows_with_swiglu(ops, m, inter, k):
     ops.gemm_rows_swiglu(dev(x, torch.bfloat16), dev(w, torch.bfloat16), act)
     want = plain.swiglu(plain.linear(x, w))
     np.testing.assert_allclose(act.float().cpu().numpy(), want, rtol=2 ** -7, atol=2 ** -7 * np.abs(want).max())
+    if inter % 8 == 0:  # the same weights with gate and up rows in turns of 8
+        turns = np.concatenate([np.concatenate([w[b:b + 8], w[inter + b:inter + b + 8]]) for b in range(0, inter, 8)])
+        again = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.gemm_rows_swiglu(dev(x, torch.bfloat16), dev(turns, torch.bfloat16), again, block=8)
+        assert torch.equal(again, act)
+
+
+def _in_turns(w, inter, block):
+    return np.concatenate([np.concatenate([w[b:b + block], w[inter + b:inter + b + block]]) for b in range(0, inter, block)])
+
+
+@pytest.mark.parametrize("m, inter, k", [(300, 128, 72), (1300, 2304, 136), (2048, 3072, 1024), (257, 384, 8)])
+def test_gemm_tc_with_swiglu(ops, m, inter, k):
+    """The tensor-core product of many rows with the activation in its epilogue (gate and up rows in turns of
+    128): against product then swiglu, and the same bits as the rows kernel gives for the first of the rows
+    where both round gate and up to bfloat16 before the activation."""
+    rng = np.random.default_rng(m + inter + k)
+    x, w = bf(rng.standard_normal((m, k))), bf(0.3 * rng.standard_normal((2 * inter, k)))
+    xd, wd = dev(x, torch.bfloat16), dev(_in_turns(w, inter, 128), torch.bfloat16)
+    act = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert ops.gemm_tc_swiglu_takes(xd, wd, act, m, 128) and not ops.gemm_tc_swiglu_takes(xd, wd, act, 256, 128)
+    ops.gemm_tc_swiglu(xd, wd, act)
+    want = plain.swiglu(plain.linear(x, w))
+    np.testing.assert_allclose(act.float().cpu().numpy(), want, rtol=2 ** -7, atol=2 ** -7 * np.abs(want).max())
+    assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
