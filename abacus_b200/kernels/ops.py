@@ -285,7 +285,6 @@ def attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cac
     """Causal attention of whole prompts (or any several tokens per sequence) against the paged bfloat16
     cache, on the tensor cores, tiles of 64 query rows (src/model.c:197-211). No window."""
     _need_cuda(qkv, out)
-    lib = load_module("attention_mma")
     n = batch.n_rows
     row = (n_heads + 2 * n_kv_heads) * head_dim
     assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
@@ -305,6 +304,7 @@ def attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cac
             _i(work.shape[0]), _i(room), _p(sc.attention_halves), _p(sc.attention_halves_tickets), _p(cache.k), _p(cache.v), _ll(pool_rows), _p(cache.page_table), _i(cache.table_width),
             _i(cache.tokens_per_page), _p(kernel_status(qkv.device)), _stream()), "attention_prefill_tc")
         return
+    lib = load_module("attention_mma")
     tiles = batch.query_tiles(64)
     _check(lib, lib.abk_attention_prefill(
         _p(qkv), _ll(row), _i(n), _p(out), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _p(tiles),
