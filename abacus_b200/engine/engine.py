@@ -46,6 +46,9 @@ def load_model(folder, dtype="bfloat16", device=None):
     return model
 
 
+_ONE_TOKEN, _WANT_IT = np.zeros(1, dtype=np.int64), [0]
+
+
 class Engine:
     def __init__(self, model, max_tokens, max_slots=None, max_context=None, use_graphs=True):
         self.model = model
@@ -116,6 +119,25 @@ class Engine:
             self.last_batch = batch
         for s in seqs:
             self.cache.advance(s.slot, len(s.tokens))
+        return logits
+
+    def step_ahead(self, slots, tokens_dev):
+        """A decode step (one token per sequence, its logits wanted) whose tokens are on the device, for instance
+        where a sampler has just put them: the host need not have seen them. tokens_dev int32 [len(slots)], in the
+        order of `slots`. Returns the logits like step(), or None if this engine runs such steps only from the
+        host (no captured graphs), in which case nothing has happened."""
+        if self.graphs is None:
+            return None
+        seqs = [Sequence(slot, _ONE_TOKEN, self.cache.length[slot], _WANT_IT) for slot in slots]
+        if len(set(slots)) != len(slots) or not self.graphs.takes(seqs):
+            return None
+        for s in seqs:
+            self.cache.reserve(s.slot, s.start + 1)
+        graph = self.graphs.get(seqs)
+        logits = graph.run(seqs, tokens_dev=tokens_dev)
+        self.last_batch = graph.batch
+        for s in seqs:
+            self.cache.advance(s.slot, 1)
         return logits
 
     def _room_for(self, n_rows, n_seqs, n_logits):

@@ -6,6 +6,13 @@ stop on a stop token (it is neither kept nor fed back), else keep the token and
 run it. The decisions of the loop (who is in which batch, who goes on, who is
 finished and why) are plain Python on the host, apart from the engine, so they
 are tested without a GPU.
+
+Where the engine can run a decode step from tokens that are still on the device (`step_ahead`), the loop
+does not let the GPU wait for the host: as soon as a step's tokens are drawn it launches the next step for
+the same sequences with them, and only then reads them (over a second stream, so that the read does not
+queue behind that step). If the tokens stop nobody, the step it launched is the next step; if they stop
+somebody, that sequence's row of it is dropped (its slot is given back anyway). A step is launched ahead
+only when no sequence ends for a reason the host knows before it sees the token (its length, its context).
 """
 import time
 from dataclasses import dataclass, field
@@ -114,6 +121,37 @@ class Generator:
             self.stats["batches"] += 1
         return requests
 
+    @staticmethod
+    def _may_run_ahead(rows, engine, max_context):
+        """Whether the next step may be launched before this step's tokens are seen: the engine can, and no
+        sequence ends with this token for a reason that does not depend on the token."""
+        if not hasattr(engine, "step_ahead"):
+            return False
+        return all(r.max_new_tokens > 0 and len(r.output) + 1 < r.max_new_tokens
+                   and len(r.prompt) + len(r.output) + 1 < max_context for r in rows)
+
+    def _read_beside(self, drawn):
+        """Start copying `drawn` (int32 on the device) to the host on a stream of its own, ordered after what the
+        current stream holds now but not after what is launched on it later. Returns a function that waits for
+        the copy and gives the list."""
+        if getattr(self, "_copy_stream", None) is None:
+            self._copy_stream = torch.cuda.Stream(drawn.device)
+            self._landing = torch.empty(4096, dtype=torch.int32).pin_memory()
+        n = drawn.numel()
+        if n > self._landing.numel():
+            return drawn.tolist
+        self._copy_stream.wait_stream(torch.cuda.current_stream(drawn.device))
+        with torch.cuda.stream(self._copy_stream):
+            self._landing[:n].copy_(drawn, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record()
+        drawn.record_stream(self._copy_stream)
+
+        def read():
+            done.synchronize()
+            return self._landing[:n].tolist()
+        return read
+
     def run_batch(self, batch):
         engine = self.engine
         for r in batch:
@@ -127,18 +165,37 @@ class Generator:
         try:
             entries = live.first_step()
             self.stats["prefill_steps"] += 1
-            while entries:
-                logits = engine.step(entries)
-                sampled = self.sampler.sample(logits, self.rng, index=engine.last_batch.seq_slot).tolist()
-                now = time.perf_counter()  # .tolist() has waited for the device
+            logits = engine.step(entries)
+            index = engine.last_batch.seq_slot  # row -> slot, on the device: which random stream a row draws from
+            while True:
+                rows = list(live.live)
+                drawn = self.sampler.sample(logits, self.rng, index=index)
+                ahead = None
+                if self._may_run_ahead(rows, engine, live.max_context):
+                    read = self._read_beside(drawn)
+                    ahead = engine.step_ahead([r.slot for r in rows], drawn)
+                    sampled = read() if ahead is not None else drawn.tolist()
+                else:
+                    sampled = drawn.tolist()
+                now = time.perf_counter()  # the tokens are on the host
                 self.stats.setdefault("t_first_token", now)
                 self.stats["t_end"] = now
                 finished, entries = live.take(sampled)
                 for r in finished:
                     engine.close(r.slot)
                     r.slot = -1
-                if entries:
-                    self.stats["decode_steps"] += 1
+                if not entries:
+                    break
+                self.stats["decode_steps"] += 1
+                if ahead is None:
+                    logits = engine.step(entries)
+                    index = engine.last_batch.seq_slot
+                elif not finished:
+                    logits, index = ahead, engine.last_batch.seq_slot
+                else:  # the step that ran ahead carries rows of sequences that have ended: the others' are the next step's
+                    keep = [i for i, r in enumerate(rows) if r.slot >= 0]
+                    logits = ahead[torch.tensor(keep, device=ahead.device)]
+                    index = torch.tensor([rows[i].slot for i in keep], dtype=torch.int32, device=ahead.device)
         finally:
             for r in batch:
                 if r.slot >= 0:

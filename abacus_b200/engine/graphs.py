@@ -70,12 +70,15 @@ class DecodeGraph:
         self.n_kernels = ops.LAUNCHES - before  # kernels one replay runs
         self.generation = model.ws.generation
 
-    def run(self, sequences):
+    def run(self, sequences, tokens_dev=None):
         """Replay for this step's sequences; returns the logits of its wanted rows (for a decode step: of
-        the first len(sequences) rows)."""
+        the first len(sequences) rows). tokens_dev (int32 on the device, one per sequence): the step's tokens,
+        instead of the sequences' own (which the host may not know yet)."""
         if self.graph is None or self.generation != self.engine.model.ws.generation:
             self.capture(sequences)
         self.batch.fill(sequences, pad_logits=True)
+        if tokens_dev is not None:
+            self.batch.tokens[:len(sequences)].copy_(tokens_dev[:len(sequences)])
         self.graph.replay()
         return self.logits[:sum(len(s.want) for s in sequences)]
 
