@@ -134,6 +134,8 @@ class Generator:
         """Start copying `drawn` (int32 on the device) to the host on a stream of its own, ordered after what the
         current stream holds now but not after what is launched on it later. Returns a function that waits for
         the copy and gives the list."""
+        if drawn.device.type != "cuda":
+            return drawn.tolist
         if getattr(self, "_copy_stream", None) is None:
             self._copy_stream = torch.cuda.Stream(drawn.device)
             self._landing = torch.empty(4096, dtype=torch.int32).pin_memory()

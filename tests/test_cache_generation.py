@@ -188,3 +188,38 @@ def test_generator_runs_batch_after_batch_and_reuses_slots():
     assert eng.steps[2] == [(0, [12]), (1, [6])] and eng.steps[3] == [(1, [7])]
     # the stop token of request 0 (13) was neither kept nor run; request 2 stopped at once
     assert eng.steps[4] == [(0, [11, 12]), (1, [40])] and eng.steps[5] == [(1, [41])]
+
+
+class FakeEngineAhead(FakeEngine):
+    """The same, but it can run a decode step from tokens it is handed as a tensor, as the real engine does from
+    tokens on the device; it notes which steps came that way."""
+
+    def __init__(self):
+        super().__init__()
+        self.ahead = []
+
+    def step_ahead(self, slots, tokens):
+        self.ahead.append(len(self.steps))
+        return self.step([(s, [int(t)], [0]) for s, t in zip(slots, tokens.tolist())])
+
+
+def test_generator_runs_ahead_and_drops_the_rows_of_sequences_that_stopped():
+    """With an engine that can step from tokens the host has not seen, the loop launches the next step before
+    it reads the tokens. Outputs and finish reasons are those of the loop that waits; a step launched ahead
+    carries the row of a sequence whose token then stopped it, and that row is dropped; no step is launched
+    ahead when a sequence is about to end by its length."""
+    eng, plain_eng = FakeEngineAhead(), FakeEngine()
+    prompts = [[10], [3, 4], [11, 12], [40]]
+    out = Generator(eng, FakeSampler(), stop_tokens=[13]).generate(prompts, max_new_tokens=4)
+    want = Generator(plain_eng, FakeSampler(), stop_tokens=[13]).generate(prompts, max_new_tokens=4)
+    assert [r.output for r in out] == [r.output for r in want] == [[11, 12], [5, 6, 7, 8], [], [41, 42, 43, 44]]
+    assert [r.finish_reason for r in out] == [r.finish_reason for r in want]
+    assert eng.opened == [0, 1, 0, 1] and eng.free == [1, 0]
+    # first batch: the prompts; a step ahead with 11 and 5; one with 12 and 6; then 13 stops request 0 after the step
+    # with 13 and 7 was launched: its row for request 0 is dropped and request 1 goes on alone (its last token by
+    # the host's way, since it ends by its length)
+    assert eng.steps[:4] == [[(0, [10]), (1, [3, 4])], [(0, [11]), (1, [5])], [(0, [12]), (1, [6])], [(0, [13]), (1, [7])]]
+    assert eng.ahead[:3] == [1, 2, 3]
+    # second batch: request 2 is stopped by its first token while the step ahead (with 13 and 41) is under way
+    assert eng.steps[4] == [(0, [11, 12]), (1, [40])] and eng.steps[5] == [(0, [13]), (1, [41])]
+    assert [len(st) for st in eng.steps[6:]] == [1, 1]
