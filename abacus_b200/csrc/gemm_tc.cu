@@ -545,9 +545,13 @@ extern "C" int abk_gemm_tc(const void *x, const void *w, void *out, int out_dtyp
     int k_blocks = (K + TILE_K - 1) / TILE_K;
     long long tiles = (long long)grid.x * grid.y;
     int splits = 1;
-    if (tiles < 112) {  // too few tiles to fill 148 SMs: share tiles along K, at least 2 k-blocks each
-        splits = (int)((148 + tiles - 1) / tiles);
-        if (splits > k_blocks / 2) splits = k_blocks / 2;
+    if (tiles < 32) {
+        // Few tiles: share them along K, but sparingly. Every split pays for its partial tile in scratch memory, a
+        // ticket and the last CTA's sum: measured at 64 rows, 32 tiles and more are fastest unsplit (9.9 us against
+        // 13.2 with two splits for 4096 x 1024), 8 tiles with four (13.8 us against 24.5 with sixteen for 1024 x 2048).
+        splits = (int)((32 + tiles - 1) / tiles);
+        if (splits > 4) splits = 4;
+        if (splits > k_blocks / 4) splits = k_blocks / 4;
         if (splits < 1) splits = 1;
     }
     if (force_splits) splits = force_splits;
