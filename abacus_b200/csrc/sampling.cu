@@ -1,9 +1,8 @@
 // Choosing the next token from float32 logits: the first maximum, or a draw from the
-// highest-k logits at a temperature (src/main.c:31-56). One block per row.
+// highest-k logits at a temperature (src/main.c:31-56). A row is cut into slices, one block each.
 #define ABK_DEFINE_ERROR
 #include "common.cuh"
 
-#define SAMPLE_THREADS 1024
 #define SAMPLE_MAX_K 64
 
 struct Best {
@@ -40,19 +39,6 @@ __device__ __forceinline__ Best block_best(Best b, Best *scratch) {
     }
     __syncthreads();
     return scratch[32];
-}
-
-// The best element that comes strictly after `prev` in the order above (prev.i < 0: the very best).
-__device__ __forceinline__ Best next_best(const float *row, int vocab, Best prev, Best *scratch) {
-    Best b;
-    b.v = -INFINITY, b.i = 0x7fffffff;
-    for (int j = threadIdx.x; j < vocab; j += blockDim.x) {
-        Best c;
-        c.v = row[j], c.i = j;
-        if (prev.i >= 0 && !before(prev, c)) continue;
-        if (before(c, b)) b = c;
-    }
-    return block_best(b, scratch);
 }
 
 // The row is cut into gridDim.x slices, one block each; the last block of a row to finish (a ticket
@@ -97,39 +83,157 @@ __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const float *__r
 
 // Draw from the top_k logits at temperature temp: p_j = exp((l_j - l_top) / temp), the random
 // number is one xorshift64 step of the row's state (src/main.c:49-55). The state is advanced.
-__global__ void __launch_bounds__(SAMPLE_THREADS) sample_topk_kernel(const float *__restrict__ logits,
-                                                                     long long row_stride, int vocab, float temp,
-                                                                     int top_k, unsigned long long *rng,
-                                                                     const int *__restrict__ rng_index,
-                                                                     int *__restrict__ out) {
-    __shared__ Best scratch[33];
-    __shared__ Best top[SAMPLE_MAX_K];
-    const float *row = logits + (long long)blockIdx.x * row_stride;
-    Best prev;
-    prev.v = 0.0f, prev.i = -1;
-    int k = top_k < vocab ? top_k : vocab;
+//
+// The row is cut into TOPK_SLICES slices, one block each. A block finds the top_k of its slice in two
+// passes: the warps' ceil(top_k / warps)-th largest thread maxima give a value that at least top_k
+// elements of the slice reach, so everything from that value up (some tens of elements) goes into
+// shared memory, and one warp picks the top_k of those in the order of src/main.c:43-48. The last
+// block of a row to finish (a ticket, left at zero) picks the top_k of the slices' and draws. `before`
+// is a total order, so nothing depends on the order in which candidates or blocks come.
+#define TOPK_SLICES 32
+#define TOPK_THREADS 256
+#define TOPK_CANDIDATES 1024
+
+// The k best of cand[0..n) in order, by one warp; what is picked is taken out (its value set to -inf, index to max).
+__device__ __forceinline__ void warp_pick(Best *cand, int n, int k, Best *picked, int lane) {
     for (int r = 0; r < k; r++) {
-        prev = next_best(row, vocab, prev, scratch);
-        if (threadIdx.x == 0) top[r] = prev;
+        Best b;
+        b.v = -INFINITY, b.i = 0x7fffffff;
+        int at = -1;
+        for (int j = lane; j < n; j += 32)
+            if (before(cand[j], b)) b = cand[j], at = j;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            Best other;
+            other.v = __shfl_xor_sync(0xffffffffu, b.v, o), other.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+            int other_at = __shfl_xor_sync(0xffffffffu, at, o);
+            if (before(other, b)) b = other, at = other_at;
+        }
+        if (lane == 0) {
+            picked[r] = b;
+            if (at >= 0) cand[at].v = -INFINITY, cand[at].i = 0x7fffffff;
+        }
+        __syncwarp();
     }
+}
+
+__global__ void __launch_bounds__(TOPK_THREADS) sample_topk_kernel(const float *__restrict__ logits, long long row_stride,
+                                                                   int vocab, float temp, int top_k,
+                                                                   unsigned long long *rng, const int *__restrict__ rng_index,
+                                                                   int *__restrict__ out, Best *part, int *tickets) {
+    __shared__ Best cand[TOPK_CANDIDATES + SAMPLE_MAX_K];  // (the last block's second half carries the first half's best along)
+    __shared__ Best picked[SAMPLE_MAX_K];
+    __shared__ Best scratch[33];
+    __shared__ float warp_bound[TOPK_THREADS / 32];
+    __shared__ int count, ticket;
+    pdl_wait();
+    const int row = blockIdx.y, slices = gridDim.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int per = (vocab + slices - 1) / slices, lo = min(vocab, blockIdx.x * per), hi = min(vocab, lo + per);
+    const float *x = logits + (long long)row * row_stride;
+    const int k = min(top_k, vocab);
+    if (threadIdx.x == 0) count = 0;
+    float bound = -INFINITY;
+    if (hi - lo > TOPK_CANDIDATES) {
+        float tmax = -INFINITY;
+        for (int j = lo + threadIdx.x; j < hi; j += TOPK_THREADS) tmax = fmaxf(tmax, x[j]);
+        // this warp's ceil(k / warps)-th largest thread maximum
+        const int rounds = (k + TOPK_THREADS / 32 - 1) / (TOPK_THREADS / 32);
+        float v = tmax, m = -INFINITY;
+        for (int r = 0; r < rounds; r++) {
+            m = warp_max(v);
+            unsigned holders = __ballot_sync(0xffffffffu, v == m);
+            if (lane == __ffs(holders) - 1) v = -INFINITY;  // one of them is taken out
+        }
+        if (lane == 0) warp_bound[warp] = m;
+        __syncthreads();
+        bound = warp_bound[0];
+        for (int w = 1; w < TOPK_THREADS / 32; w++) bound = fminf(bound, warp_bound[w]);
+    } else {
+        __syncthreads();
+    }
+    for (int j = lo + threadIdx.x; j < hi; j += TOPK_THREADS) {
+        const float v = x[j];
+        if (v >= bound) {
+            const int at = atomicAdd(&count, 1);
+            if (at < TOPK_CANDIDATES) cand[at].v = v, cand[at].i = j;
+        }
+    }
+    __syncthreads();
+    Best *mine = part + ((long long)row * slices + blockIdx.x) * SAMPLE_MAX_K;
+    if (count <= TOPK_CANDIDATES) {
+        if (warp == 0) {
+            warp_pick(cand, count, k, picked, lane);
+            for (int r = lane; r < k; r += 32) mine[r] = picked[r];
+        }
+    } else {  // (many equal logits at the top: more candidates than there is room for) one at a time, from the slice itself
+        Best prev;
+        prev.v = 0.0f, prev.i = -1;
+        for (int r = 0; r < k; r++) {
+            Best b;
+            b.v = -INFINITY, b.i = 0x7fffffff;
+            for (int j = lo + threadIdx.x; j < hi; j += TOPK_THREADS) {
+                Best c;
+                c.v = x[j], c.i = j;
+                if (prev.i >= 0 && !before(prev, c)) continue;
+                if (before(c, b)) b = c;
+            }
+            prev = block_best(b, scratch);
+            if (threadIdx.x == 0) mine[r] = prev;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) ticket = atomicAdd(&tickets[row], 1);
+    __syncthreads();
+    if (ticket != slices - 1) return;
+    __threadfence();
+    // the last block of the row: the best k of the slices' best k
+    const int n = slices * k;  // at most 32 * 64
+    Best *all = cand;          // TOPK_CANDIDATES holds 32 x 32; more go through in two halves below
+    if (n <= TOPK_CANDIDATES) {
+        for (int j = threadIdx.x; j < n; j += TOPK_THREADS) {
+            const volatile Best *q = part + ((long long)row * slices + j / k) * SAMPLE_MAX_K + j % k;
+            all[j].v = q->v, all[j].i = q->i;
+        }
+        __syncthreads();
+        if (warp == 0) warp_pick(all, n, k, picked, lane);
+    } else {
+        // first the lower half of the slices, then its k best together with the upper half
+        const int half = slices / 2 * k;
+        for (int j = threadIdx.x; j < half; j += TOPK_THREADS) {
+            const volatile Best *q = part + ((long long)row * slices + j / k) * SAMPLE_MAX_K + j % k;
+            all[j].v = q->v, all[j].i = q->i;
+        }
+        __syncthreads();
+        if (warp == 0) warp_pick(all, half, k, picked, lane);
+        __syncthreads();
+        for (int j = threadIdx.x; j < n - half; j += TOPK_THREADS) {
+            const volatile Best *q = part + ((long long)row * slices + (half + j) / k) * SAMPLE_MAX_K + (half + j) % k;
+            all[j].v = q->v, all[j].i = q->i;
+        }
+        for (int j = threadIdx.x; j < k; j += TOPK_THREADS) all[n - half + j] = picked[j];
+        __syncthreads();
+        if (warp == 0) warp_pick(all, n - half + k, k, picked, lane);
+    }
+    __syncthreads();
     if (threadIdx.x != 0) return;
+    tickets[row] = 0;
     float p[SAMPLE_MAX_K], sum = 0.0f;
-    for (int j = 0; j < k; j++) sum += p[j] = expf((top[j].v - top[0].v) / temp);
-    int which = rng_index ? rng_index[blockIdx.x] : blockIdx.x;  // e.g. the row's cache slot
+    for (int j = 0; j < k; j++) sum += p[j] = expf((picked[j].v - picked[0].v) / temp);
+    int which = rng_index ? rng_index[row] : row;  // e.g. the row's cache slot
     unsigned long long s = rng[which];
     s ^= s << 13, s ^= s >> 7, s ^= s << 17;
     rng[which] = s;
     float r = (float)(s >> 40) / (float)(1 << 24) * sum;
-    int chosen = top[k - 1].i;
+    int chosen = picked[k - 1].i;
     for (int j = 0; j < k; j++)
         if ((r -= p[j]) <= 0.0f) {
-            chosen = top[j].i;
+            chosen = picked[j].i;
             break;
         }
-    out[blockIdx.x] = chosen;
+    out[row] = chosen;
 }
 
-// scratch: 8 * ARGMAX_SLICES * n_rows bytes; tickets: int32 [n_rows], zero before and after.
 extern "C" int abk_argmax_slices() { return ARGMAX_SLICES; }
 extern "C" int abk_argmax(const float *logits, long long row_stride, int n_rows, int vocab, int *out, void *scratch,
                           int *tickets, void *stream) {
@@ -142,13 +246,19 @@ extern "C" int abk_argmax(const float *logits, long long row_stride, int n_rows,
     return ABK_LAUNCH_RESULT();
 }
 
+// scratch: room for abk_sample_topk_scratch_bytes(n_rows) bytes; tickets: int32 [n_rows], zero before and after.
+extern "C" long long abk_sample_topk_scratch_bytes(int n_rows) { return (long long)n_rows * TOPK_SLICES * SAMPLE_MAX_K * sizeof(Best); }
 extern "C" int abk_sample_topk(const float *logits, long long row_stride, int n_rows, int vocab, float temp, int top_k,
-                               unsigned long long *rng, const int *rng_index, int *out, void *stream) {
+                               unsigned long long *rng, const int *rng_index, int *out, void *scratch, int *tickets,
+                               void *stream) {
     if (n_rows <= 0) return 0;
     if (vocab < 1) ABK_REFUSE("sample: vocabulary of %d", vocab);
     if (top_k < 1 || top_k > SAMPLE_MAX_K) ABK_REFUSE("sample: top_k %d is not in 1..%d", top_k, SAMPLE_MAX_K);
     if (!(temp > 0.0f)) ABK_REFUSE("sample: temperature %g is not positive (use argmax)", temp);
-    sample_topk_kernel<<<n_rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, row_stride, vocab, temp, top_k, rng,
-                                                                           rng_index, out);
+    if (n_rows > 65535) ABK_REFUSE("sample: %d rows exceed a grid", n_rows);
+    int slices = TOPK_SLICES;
+    while (slices > 1 && (vocab + slices - 1) / slices < TOPK_THREADS) slices >>= 1;  // a small vocabulary: fewer slices
+    abk_launch(sample_topk_kernel, dim3(slices, n_rows), dim3(TOPK_THREADS), 0, (cudaStream_t)stream, logits, row_stride, vocab,
+               temp, top_k, rng, rng_index, out, (Best *)scratch, tickets);
     return ABK_LAUNCH_RESULT();
 }

@@ -257,8 +257,12 @@ def sample_topk(logits, temperature, top_k, rng_state, out, n_rows=None, rng_ind
     assert rng_state.dtype == torch.int64 and out.numel() >= n
     assert rng_index is None or (rng_index.dtype == torch.int32 and rng_index.numel() >= n)
     assert rng_index is not None or rng_state.numel() >= n
+    sc = _Scratch.of(logits.device)
+    if n > sc.sample_rows:
+        raise KernelRefused(f"sample_topk: {n} rows are more than the scratch of {sc.sample_rows} rows")
     _check(lib, lib.abk_sample_topk(_p(logits), _ll(logits.stride(0)), _i(n), _i(logits.shape[1]), _f(temperature),
-                                    _i(top_k), _p(rng_state), _p(rng_index), _p(out), _stream()), "sample_topk")
+                                    _i(top_k), _p(rng_state), _p(rng_index), _p(out), _p(sc.sample_part),
+                                    _p(sc.sample_tickets), _stream()), "sample_topk")
 
 
 def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, ws=None):
@@ -404,6 +408,20 @@ class _Scratch:
     def argmax_part(self):
         return self._lazy("argmax_part", lambda: torch.empty(
             self.argmax_rows * load_module("sampling").abk_argmax_slices() * 2, dtype=torch.float32, device=self.device))
+
+    sample_rows = 1024
+
+    @property
+    def sample_part(self):
+        def make():
+            lib = load_module("sampling")
+            lib.abk_sample_topk_scratch_bytes.restype = ctypes.c_longlong
+            return torch.empty(lib.abk_sample_topk_scratch_bytes(_i(self.sample_rows)), dtype=torch.uint8, device=self.device)
+        return self._lazy("sample_part", make)
+
+    @property
+    def sample_tickets(self):
+        return self._lazy("sample_tickets", lambda: torch.zeros(self.sample_rows, dtype=torch.int32, device=self.device))
 
     @property
     def argmax_tickets(self):

@@ -144,6 +144,33 @@ def test_sample_topk_draws_what_the_plain_sampler_draws(ops, temp, top_k):
         ops.sample_topk(ld, 0.0, 5, st, out)
 
 
+@pytest.mark.parametrize("top_k", [20, 64])
+def test_sample_topk_on_a_large_vocabulary(ops, top_k):
+    """Slices of more than a thousand logits take the two-pass way (a bound from the threads' maxima, then the
+    candidates above it): random rows, the top spread over slices or crowded into one, ties across slices, and
+    rows with so many equal logits at the top that the candidates overflow and the slice is searched one by one."""
+    rng = np.random.default_rng(5)
+    vocab, rows, temp = 70001, 7, 0.8
+    logits = (2 * rng.standard_normal((rows, vocab))).astype(np.float32)
+    logits[1, 30000:30100] += 9.0                       # the whole top in one slice
+    logits[2, [5, 2200, 40000, 69999]] = 11.0           # equal maxima in four slices
+    logits[3, :] = -2.5                                 # all equal: the first top_k indices, by the slow way
+    logits[4, 1000:4000] = 7.0                          # three thousand equal maxima: overflow in two slices
+    logits[5, :] = np.float32(-np.inf)
+    logits[5, 123], logits[5, 60000] = 0.5, 0.25        # fewer finite logits than top_k
+    states = [int(s) for s in rng.integers(1, 2 ** 62, rows)]
+    st, want_states = dev(states, torch.int64), list(states)
+    ld, out = dev(logits), torch.empty(rows, dtype=torch.int32, device="cuda")
+    for step in range(4):
+        ops.sample_topk(ld, temp, top_k, st, out)
+        got = out.tolist()
+        for r in range(rows):
+            tok, want_states[r] = plain.sample(logits[r], temp, want_states[r], top_k)
+            assert got[r] == tok, (step, r)
+    from abacus_b200.kernels.ops import _Scratch
+    assert int(_Scratch.of(torch.device("cuda", 0)).sample_tickets.abs().sum()) == 0
+
+
 # ------------------------------------------------------------------ q/k/v preparation and attention
 
 class Harness:
