@@ -90,17 +90,17 @@ static inline bool abk_pdl_enabled() {
     }
     return on != 0;
 }
-// cluster_x > 1: the grid's CTAs come as clusters of that many along x (grid.x must be a multiple of it).
+// The grid's CTAs come as clusters of `cluster` CTAs (each grid dimension must be a multiple of the cluster's).
 template <typename... KArgs, typename... Args>
 static inline void abk_launch_clusters(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                       int cluster_x, Args &&...args) {
+                                       dim3 cluster, Args &&...args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int n = 0;
-    if (cluster_x > 1) {
+    if (cluster.x * cluster.y * cluster.z > 1) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = cluster_x, attr[n].val.clusterDim.y = 1, attr[n].val.clusterDim.z = 1;
+        attr[n].val.clusterDim.x = cluster.x, attr[n].val.clusterDim.y = cluster.y, attr[n].val.clusterDim.z = cluster.z;
         n++;
     }
     if (abk_pdl_enabled()) {
@@ -112,9 +112,14 @@ static inline void abk_launch_clusters(void (*kernel)(KArgs...), dim3 grid, dim3
     cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);  // the error, if any, is read by ABK_LAUNCH_RESULT
 }
 template <typename... KArgs, typename... Args>
+static inline void abk_launch_clusters(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                       int cluster_x, Args &&...args) {
+    abk_launch_clusters(kernel, grid, block, smem, stream, dim3(cluster_x, 1, 1), std::forward<Args>(args)...);
+}
+template <typename... KArgs, typename... Args>
 static inline void abk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               Args &&...args) {
-    abk_launch_clusters(kernel, grid, block, smem, stream, 1, std::forward<Args>(args)...);
+    abk_launch_clusters(kernel, grid, block, smem, stream, dim3(1, 1, 1), std::forward<Args>(args)...);
 }
 #endif
 

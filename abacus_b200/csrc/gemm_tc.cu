@@ -13,8 +13,11 @@
 // BN columns (16..64) and no tensor-core work is spent on padding. The weights stream through
 // once either way.
 //
-// Split K: grid.z CTAs share a tile, each over its own K range. Each writes its float32 partial
-// tile to scratch memory and takes a ticket; the last one adds the partials in split order
+// Split K: grid.z CTAs share a tile, each over its own K range. Up to 8 of them (and column tiles up to
+// 128) are a thread-block cluster: each leaves its float32 partial tile in its own shared memory, where
+// the operands were, and after a cluster barrier adds up a share of the columns over all partial tiles,
+// in split order, reading the others' through distributed shared memory. Otherwise each writes its
+// partial tile to scratch memory and takes a ticket, and the last one adds the partials in split order
 // (so the result does not depend on which CTA came last) and stores the tile.
 //
 // Many rows and many tiles (a prompt): the persistent kernel below. One CTA to an SM walks over the
@@ -43,6 +46,7 @@ struct GemmTc {
     int *tickets;     // [tiles], zero before and after the launch
     int *status;
     int vec;  // stride_q == 1 and every 16-column run of a row starts on a 16-byte boundary
+    int in_cluster;  // the splits of a tile are a thread-block cluster and add up through distributed shared memory
 };
 
 template <int BN, int STAGES> struct GemmSmem {
@@ -143,7 +147,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
         tc::fence_after_sync();
         const int tiles = gridDim.x * gridDim.y, tile = blockIdx.y * gridDim.x + blockIdx.x;
         const bool direct = g.splits == 1;
-        float *mine = direct ? nullptr : g.partials + ((long long)split * tiles + tile) * (BN * TILE_P);
+        float *mine = direct || g.in_cluster ? nullptr : g.partials + ((long long)split * tiles + tile) * (BN * TILE_P);
         TO *out = (TO *)g.out;
         if (ok) {
 #pragma unroll 1
@@ -151,7 +155,11 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
                 uint32_t v[16];
                 tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + c0, v);
                 tc::tmem_ld_wait();
-                if (direct && g.vec && p < g.P && q0 + c0 + 16 <= g.Q) {
+                if (g.in_cluster) {  // the operands' stages are free: every product has read them
+                    float *at = (float *)smem + row * (BN + 4) + c0;
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4) *(uint4 *)(at + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                } else if (direct && g.vec && p < g.P && q0 + c0 + 16 <= g.Q) {
                     store16(out + (long long)p * g.stride_p + q0 + c0, v);
                 } else if (direct) {
                     if (p < g.P) {
@@ -167,7 +175,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
                 }
             }
         }
-        if (!direct) {
+        if (!direct && !g.in_cluster) {
             // the last CTA of this tile to get here adds up all partials, in split order
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -207,6 +215,31 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
                 if (threadIdx.x == 64) g.tickets[tile] = 0;
             }
         }
+    }
+    if (g.in_cluster) {
+        // every CTA of the tile adds up its share of the columns (groups of four) over all partial tiles, in split order
+        tc::cluster_sync();
+        if (warp >= 2) {
+            const int quarter = warp & 3, row = quarter * 32 + lane, p = p0 + row;
+            const int groups = BN / 4, per = (groups + g.splits - 1) / g.splits;
+            const uint32_t base = tc::smem_addr((float *)smem + row * (BN + 4));
+            TO *out = (TO *)g.out;
+            for (int gi = split * per; gi < min(groups, (split + 1) * per); gi++) {
+                float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int s0 = 0; s0 < g.splits; s0++) {
+                    const float4 t = tc::ld_cluster_f4(tc::peer_smem(base + gi * 16, s0));
+                    sum.x += t.x, sum.y += t.y, sum.z += t.z, sum.w += t.w;
+                }
+                const float r4[4] = {sum.x, sum.y, sum.z, sum.w};
+                if (p < g.P) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        if (q0 + gi * 4 + j < g.Q)
+                            out[(long long)p * g.stride_p + (long long)(q0 + gi * 4 + j) * g.stride_q] = from_float<TO>(r4[j]);
+                }
+            }
+        }
+        tc::cluster_sync();  // nobody leaves while its partial tile may still be read
     }
     tc::fence_before_sync();
     __syncthreads();
@@ -446,7 +479,7 @@ static int launch(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g,
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    abk_launch(kernel, grid, dim3(GEMM_THREADS), (size_t)bytes, s, mp, mq, g);
+    abk_launch_clusters(kernel, grid, dim3(GEMM_THREADS), (size_t)bytes, s, dim3(1, 1, g.in_cluster ? g.splits : 1), mp, mq, g);
     return ABK_LAUNCH_RESULT();
 }
 
@@ -545,13 +578,13 @@ extern "C" int abk_gemm_tc(const void *x, const void *w, void *out, int out_dtyp
     int k_blocks = (K + TILE_K - 1) / TILE_K;
     long long tiles = (long long)grid.x * grid.y;
     int splits = 1;
-    if (tiles < 32) {
-        // Few tiles: share them along K, but sparingly. Every split pays for its partial tile in scratch memory, a
-        // ticket and the last CTA's sum: measured at 64 rows, 32 tiles and more are fastest unsplit (9.9 us against
-        // 13.2 with two splits for 4096 x 1024), 8 tiles with four (13.8 us against 24.5 with sixteen for 1024 x 2048).
-        splits = (int)((32 + tiles - 1) / tiles);
-        if (splits > 4) splits = 4;
+    if (tiles <= 32) {
+        // Few tiles: share them along K, but sparingly: every split pays for its partial tile and for adding them
+        // up. Measured at 64 rows with the splits as a cluster: 8 tiles (1024 x 2048) 14.3 us unsplit, 8.5 with four;
+        // 32 tiles (4096 x 1024) 9.6 us unsplit, 8.6 with four; 48 tiles (6144 x 1024) 9.9 us unsplit, 12.0 with four.
+        splits = 4;
         if (splits > k_blocks / 4) splits = k_blocks / 4;
+        if (bn > 128 && tiles >= 16) splits = 1;  // (partial tiles through scratch memory: 2048 x 4096 x 1024 at 200 rows doubles)
         if (splits < 1) splits = 1;
     }
     if (force_splits) splits = force_splits;
@@ -576,6 +609,8 @@ extern "C" int abk_gemm_tc(const void *x, const void *w, void *out, int out_dtyp
     g.stride_p = swap ? 1 : ldo, g.stride_q = swap ? ldo : 1;
     g.k_blocks = k_blocks, g.k_blocks_per_split = per, g.splits = splits;
     g.partials = scratch, g.tickets = tickets, g.status = status;
+    // (a partial tile of 128 x (bn + 4) floats fits where the operands' stages were for column tiles up to 128)
+    g.in_cluster = splits > 1 && splits <= 8 && bn <= 128;
     int esize = out_dtype == ABK_BF16 ? 2 : 4;
     g.vec = !swap && ((uintptr_t)out % 16 == 0) && (ldo * esize) % 16 == 0;
     cudaStream_t s = (cudaStream_t)stream;
