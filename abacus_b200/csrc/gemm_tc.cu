@@ -47,6 +47,7 @@ struct GemmTc {
     int *status;
     int vec;  // stride_q == 1 and every 16-column run of a row starts on a 16-byte boundary
     int in_cluster;  // the splits of a tile are a thread-block cluster and add up through distributed shared memory
+    int weights_are_p;  // which operand is nobody's output (the weights): its first stages are asked for before pdl_wait()
 };
 
 template <int BN, int STAGES> struct GemmSmem {
@@ -100,20 +101,29 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = *tmem_holder;
-    pdl_wait();  // barriers, tensor memory and the tensor maps are ready; now the operands may be read
-
+    // barriers, tensor memory and the tensor maps are ready. The weights' first stages are asked for at once; what
+    // the kernel before this one writes (the other operand) only after pdl_wait().
     if (warp == 0) {
         if (lane == 0) {
+            const int ahead = min(STAGES, kb_end - kb_begin);
+            for (int i = 0; i < ahead; i++) {
+                tc::mbar_expect_tx(&full[i], S::A_BYTES + S::B_BYTES);
+                if (g.weights_are_p) tc::tma_load_2d(a_tiles + i * S::A_BYTES, &map_p, (kb_begin + i) * TILE_K, p0, &full[i]);
+                else tc::tma_load_2d(b_tiles + i * S::B_BYTES, &map_q, (kb_begin + i) * TILE_K, q0, &full[i]);
+            }
+            pdl_wait();
             int issued = 0;
             for (int kb = kb_begin; kb < kb_end; kb++, issued++) {
                 int s = issued % STAGES;
-                if (!tc::mbar_wait(&empty[s], ((issued / STAGES) & 1) ^ 1)) {
-                    flags[0] = 1;
-                    break;
+                if (issued >= ahead) {
+                    if (!tc::mbar_wait(&empty[s], ((issued / STAGES) & 1) ^ 1)) {
+                        flags[0] = 1;
+                        break;
+                    }
+                    tc::mbar_expect_tx(&full[s], S::A_BYTES + S::B_BYTES);
                 }
-                tc::mbar_expect_tx(&full[s], S::A_BYTES + S::B_BYTES);
-                tc::tma_load_2d(a_tiles + s * S::A_BYTES, &map_p, kb * TILE_K, p0, &full[s]);
-                tc::tma_load_2d(b_tiles + s * S::B_BYTES, &map_q, kb * TILE_K, q0, &full[s]);
+                if (issued >= ahead || !g.weights_are_p) tc::tma_load_2d(a_tiles + s * S::A_BYTES, &map_p, kb * TILE_K, p0, &full[s]);
+                if (issued >= ahead || g.weights_are_p) tc::tma_load_2d(b_tiles + s * S::B_BYTES, &map_q, kb * TILE_K, q0, &full[s]);
             }
             if (flags[0]) {  // let the copies still in flight land before the CTA's memory goes away
                 for (int i = max(0, issued - STAGES); i < issued; i++) tc::mbar_wait(&full[i % STAGES], (i / STAGES) & 1);
@@ -286,22 +296,31 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_persistent_kernel(const 
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = *tmem_holder;
-    pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
+            // the weights (the columns' operand) of the first tile's first stages are asked for before pdl_wait():
+            // nobody writes them; the rows' operand comes from the kernel before
+            const int ahead = min(STAGES, g.k_blocks);
+            for (int i = 0; i < ahead; i++) {
+                tc::mbar_expect_tx(&full[i], S::A_BYTES + S::B_BYTES);
+                tc::tma_load_2d(b_tiles + i * S::B_BYTES, &map_q, i * TILE_K, ((int)blockIdx.x / m_tiles) * BN, &full[i]);
+            }
+            pdl_wait();
             int issued = 0;
             for (int t = blockIdx.x; t < tiles && !flags[0]; t += gridDim.x) {
                 const int p0 = (t % m_tiles) * TILE_P, q0 = (t / m_tiles) * BN;
                 for (int kb = 0; kb < g.k_blocks; kb++, issued++) {
                     int s = issued % STAGES;
-                    if (!tc::mbar_wait(&empty[s], ((issued / STAGES) & 1) ^ 1)) {
-                        flags[0] = 1;
-                        break;
+                    if (issued >= ahead) {
+                        if (!tc::mbar_wait(&empty[s], ((issued / STAGES) & 1) ^ 1)) {
+                            flags[0] = 1;
+                            break;
+                        }
+                        tc::mbar_expect_tx(&full[s], S::A_BYTES + S::B_BYTES);
+                        tc::tma_load_2d(b_tiles + s * S::B_BYTES, &map_q, kb * TILE_K, q0, &full[s]);
                     }
-                    tc::mbar_expect_tx(&full[s], S::A_BYTES + S::B_BYTES);
                     tc::tma_load_2d(a_tiles + s * S::A_BYTES, &map_p, kb * TILE_K, p0, &full[s]);
-                    tc::tma_load_2d(b_tiles + s * S::B_BYTES, &map_q, kb * TILE_K, q0, &full[s]);
                 }
             }
             if (flags[0]) {  // let the copies still in flight land before the CTA's memory goes away
@@ -341,6 +360,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_persistent_kernel(const 
         const int quarter = warp & 3, row = quarter * 32 + lane;
         TO *out = (TO *)g.out;
         int it = 0;
+        pdl_wait();  // (what they store comes after the loads that wait anyway; this keeps the rule simple)
         for (int t = blockIdx.x; t < tiles; t += gridDim.x, it++) {
             const int b = it & 1;
             const int p = (t % m_tiles) * TILE_P + row, q0 = (t / m_tiles) * BN;
@@ -513,7 +533,7 @@ extern "C" int abk_gemm_tc_swiglu(const void *x, const void *w, void *act, int M
     GemmTc g;
     g.out = act, g.P = M, g.Q = N, g.K = K, g.stride_p = ldo, g.stride_q = 1;
     g.k_blocks = (K + TILE_K - 1) / TILE_K, g.k_blocks_per_split = g.k_blocks, g.splits = 1;
-    g.partials = nullptr, g.tickets = nullptr, g.status = status, g.vec = 1;
+    g.partials = nullptr, g.tickets = nullptr, g.status = status, g.vec = 1, g.in_cluster = 0, g.weights_are_p = 0;
     const int m_tiles = (M + TILE_P - 1) / TILE_P, tiles = m_tiles * (N / 128);
     auto kernel = gemm_tc_persistent_kernel<256, 4, __nv_bfloat16, true>;
     static bool configured = false;
@@ -611,6 +631,7 @@ extern "C" int abk_gemm_tc(const void *x, const void *w, void *out, int out_dtyp
     g.partials = scratch, g.tickets = tickets, g.status = status;
     // (a partial tile of 128 x (bn + 4) floats fits where the operands' stages were for column tiles up to 128)
     g.in_cluster = splits > 1 && splits <= 8 && bn <= 128;
+    g.weights_are_p = swap ? 1 : 0;
     int esize = out_dtype == ABK_BF16 ? 2 : 4;
     g.vec = !swap && ((uintptr_t)out % 16 == 0) && (ldo * esize) % 16 == 0;
     cudaStream_t s = (cudaStream_t)stream;
