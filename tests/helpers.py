@@ -11,8 +11,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
 
 # Four tiny configurations of the architecture that differ in every size and option.
-#   A: BASELINE config 0 (tied head, group of 2, norm weights 1).
-#   B: BASELINE config 1 (untied head, group of 3, head size decoupled from the width, prime vocabulary).
+#   A: the first measured configuration in small (tied head, group of 2, norm weights 1).
+#   B: the second in small (untied head, group of 3, head size decoupled from the width, prime vocabulary).
 #   C: one kv head per query head, head size 48, a window of 24 keys on every other layer.
 TINY = {
     "A": dict(cfg=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,

@@ -217,7 +217,7 @@ def test_prompt_steps_of_a_shape_seen_before_are_replayed(tmp_path, name, dname,
 @pytest.mark.parametrize("dname", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_greedy_generation_through_the_entry_point(tmp_path, name, dname):
-    """BASELINE workloads: unequal prompts, greedy; more requests than one batch holds, a stop token."""
+    """The workloads that are measured: unequal prompts, greedy; more requests than one batch holds, a stop token."""
     from abacus_b200 import LM
     folder = make_model_folder(tmp_path, name)
     cfg, w = plain.load(folder)
@@ -249,7 +249,7 @@ def test_greedy_generation_through_the_entry_point(tmp_path, name, dname):
 
 
 def test_sampled_generation_is_seeded_and_independent_of_batching(tmp_path):
-    """BASELINE config 1's workload: temperature 0.8, seeded. A request draws the same tokens alone
+    """The second measured configuration's workload: temperature 0.8, seeded. A request draws the same tokens alone
     as in a batch, because its random stream is its own."""
     from abacus_b200 import LM
     folder = make_model_folder(tmp_path, "B")
