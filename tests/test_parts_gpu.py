@@ -212,6 +212,46 @@ def test_prompt_steps_of_a_shape_seen_before_are_replayed(tmp_path, name, dname,
     assert engine.prompt_graphs.captured == 2 and engine.prompt_graphs.replayed == 4 and eager.prompt_graphs is None
 
 
+def test_layers_of_the_measured_size(tmp_path):
+    """Two layers with the sizes of the measured configuration (width 1024, 16 / 8 heads of 128, inner size 3072), a
+    prompt of 2,048 tokens beside one of 700, then decode steps: the step takes the ways that tiny models do not
+    (the persistent tensor-core product, SwiGLU in its epilogue, attention tiles halved between CTAs, the rows
+    kernels with clusters), the second time from a captured graph. bfloat16 against the plain implementation."""
+    from abacus_b200.config import Qwen3Config
+    from abacus_b200.engine import Engine, load_model
+    from abacus_b200.weights import write_random_model
+    from helpers import SHARP
+    raw = dict(hidden_size=1024, intermediate_size=3072, num_hidden_layers=2, num_attention_heads=16,
+               num_key_value_heads=8, head_dim=128, vocab_size=3000, max_position_embeddings=4096, rope_theta=1e6,
+               rms_norm_eps=1e-6, tie_word_embeddings=True, architectures=["Qwen3ForCausalLM"], model_type="qwen3")
+    folder = os.path.join(str(tmp_path), "wide")
+    # (the factors that sharpen the tiny models, with the embedding's turned down: at this width it alone
+    # would make logits of twenty and more, where the tiny models have five to eight)
+    write_random_model(folder, Qwen3Config.from_dict(raw), seed=5, norm_std=0.05, scales=dict(SHARP, embed_tokens=4.0))
+    pcfg, pw = plain.load(folder)
+    rng = np.random.default_rng(3)
+    lens, extra = (2048, 700), 2
+    ids = [random_tokens(rng, n + extra, pcfg["vocab"]) for n in lens]
+    exact = [plain.forward(pcfg, pw, t) for t in ids]
+    want = [plain.forward(pcfg, pw, t, rnd=plain.bf16_round) for t in ids]
+    noise = [float(np.abs(w - e).max()) for w, e in zip(want, exact)]
+    engine = Engine(load_model(folder, "bfloat16"), max_tokens=2 * 4096)
+    for turn in range(2):
+        slots = [engine.open() for _ in ids]
+        places = [[0, 100, n // 2, n - 1] for n in lens]
+        got = engine.step([(s, t[:n], w) for s, t, n, w in zip(slots, ids, lens, places)]).cpu().numpy()
+        for i, w in enumerate(places):
+            assert_logits(got[4 * i:4 * i + 4], want[i][w], "bfloat16", f"turn {turn} prompt {i}", noise[i])
+        for step in range(extra):
+            got = engine.step([(s, t[n + step:n + step + 1], [0]) for s, t, n in zip(slots, ids, lens)]).cpu().numpy()
+            for i, n in enumerate(lens):
+                assert_logits(got[i:i + 1], want[i][n + step:n + step + 1], "bfloat16", f"turn {turn} decode {step} of {i}", noise[i])
+        for s in slots:
+            engine.close(s)
+    engine.check_status()
+    assert engine.prompt_graphs.replayed == 1
+
+
 # ------------------------------------------------------------------ generation through the entry point
 
 @pytest.mark.parametrize("dname", ["float32", "bfloat16"])
