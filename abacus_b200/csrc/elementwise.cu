@@ -284,6 +284,60 @@ template <typename T> __global__ void qkv_prep_kernel(QkvPrep p) {
 // read and written as one vector each, with no shared-memory staging.
 #define FAST_WARPS 4
 #define FAST_SLOTS 4  // groups of heads a warp has in flight at a time (its share of a prompt token's 32 heads of 128)
+// One head of one token in the fast kernels: this lane's 8 elements `raw` of head `head` (q, k or v by its number) are
+// normed, rotated with the lane's angles cs/sn, written back to the row, and k and v go to the cache at kept_at (the
+// token's place in the pools for kv head 0; negative: not kept). Whole warps call it (shuffles); lanes past the
+// end of the heads have live = false.
+template <int HD>
+__device__ __forceinline__ void prep_head(const QkvPrep &p, uint4 raw_u, int head, bool live, int l, bool upper,
+                                          const float *cs, const float *sn, __nv_bfloat16 *row0, long long kept_at) {
+    constexpr int LPH = HD / 8;
+    const bool is_q = head < p.n_heads, is_k = !is_q && head < p.n_heads + p.n_kv_heads;
+    const int kv_head = is_q ? 0 : is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
+    const uint32_t in[4] = {raw_u.x, raw_u.y, raw_u.z, raw_u.w};
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const float2 f = __bfloat1622float2(*(const __nv_bfloat162 *)&in[e]);
+        v[2 * e] = f.x, v[2 * e + 1] = f.y;
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; e++) ss += v[e] * v[e];
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);  // over the head's lanes
+    const float *w = is_q ? p.q_norm : p.k_norm;
+    if ((is_q || is_k) && w) {
+        const float scale = 1.0f / sqrtf(ss / (float)HD + p.eps);
+        const float4 w0 = __ldg((const float4 *)(w + l * 8)), w1 = __ldg((const float4 *)(w + l * 8 + 4));
+        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[e] = wv[e] * (v[e] * scale);
+    }
+    // the element HD / 2 above or below each of this lane's, from the lane that holds it
+    float other[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) other[e] = __shfl_xor_sync(0xffffffffu, v[e], LPH / 2);
+    uint32_t outw[4] = {in[0], in[1], in[2], in[3]};
+    if (is_q || is_k) {
+        if (p.cos) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = upper ? v[e] * cs[e] + other[e] * sn[e] : v[e] * cs[e] - other[e] * sn[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+            outw[e] = *(uint32_t *)&h2;
+        }
+        if (live) *(uint4 *)(row0 + (long long)head * HD) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+    }
+    if (live && !is_q && kept_at >= 0) {
+        __nv_bfloat16 *dst = (__nv_bfloat16 *)(is_k ? p.k_pool : p.v_pool) + kept_at +
+                             (long long)kv_head * p.cache.tokens_per_page * HD + l * 8;
+        *(uint4 *)dst = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+    }
+}
+
 // bfloat16, head sizes 64, 128 and 256, rotation over the whole head in halves: a lane holds 8 consecutive
 // elements (16 bytes) of a head, so HD / 8 lanes hold a head and a warp 32 * 8 / HD heads at a time. A CTA
 // takes `heads_per_cta` heads of one token (q, then k, then v): all of them for a prompt, where the
@@ -339,51 +393,86 @@ template <int HD> __global__ void __launch_bounds__(FAST_WARPS * 32) qkv_prep_fa
         for (int u = 0; u < FAST_SLOTS; u++) {
             const int head = h0 + u * FAST_WARPS * HPW;
             if (head - sub >= limit) break;  // the whole warp is past the end (the shuffles below are for whole warps)
-            const bool live = head < limit;
-            const bool is_q = head < p.n_heads, is_k = !is_q && head < p.n_heads + p.n_kv_heads;
-            const int kv_head = is_q ? 0 : is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
-            const uint32_t in[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-            float v[8];
+            prep_head<HD>(p, raw[u], head, head < limit, l, upper, cs, sn, row0, kept_at);
+        }
+    }
+}
+
+// The same for the many tokens of a prompt. One token to a CTA gives more CTAs than the GPU holds at a time, and
+// every wave of them walks the chain token -> sequence -> slot -> page -> rows anew. Here a CTA takes PROMPT_TOKENS
+// tokens in a row: it looks up the indices, pages and angles of all of them at once, before pdl_wait() (they are
+// written by kernels further back than the one just before), and then streams the rows, loading the next
+// token's while it works on this one's, so that all the CTAs of a prompt of a few thousand tokens are resident
+// together and the chain is walked once.
+#define PROMPT_TOKENS 4
+template <int HD> __global__ void __launch_bounds__(FAST_WARPS * 32) qkv_prep_prompt_kernel(QkvPrep p, int n_tokens) {
+    constexpr int LPH = HD / 8, HPW = 32 / LPH, ROUND = FAST_WARPS * HPW * FAST_SLOTS;  // heads of a token a CTA has in flight
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane / LPH, l = lane % LPH;
+    const bool upper = l >= LPH / 2;
+    const int total_heads = p.n_heads + 2 * p.n_kv_heads;
+    const int limit = p.q_only ? p.n_heads : total_heads;
+    const int rounds = (limit + ROUND - 1) / ROUND;
+    const int t0 = blockIdx.x * PROMPT_TOKENS;
+    const int at = (upper ? l - LPH / 2 : l) * 8;
+    const bool caching = !p.q_only && p.k_pool;
+    int seq[PROMPT_TOKENS], pos[PROMPT_TOKENS], slot[PROMPT_TOKENS], len_after[PROMPT_TOKENS];
+    long long kept[PROMPT_TOKENS];
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const float2 f = __bfloat1622float2(*(const __nv_bfloat162 *)&in[e]);
-                v[2 * e] = f.x, v[2 * e + 1] = f.y;
-            }
-            float ss = 0.0f;
+    for (int i = 0; i < PROMPT_TOKENS; i++) {
+        const bool in = t0 + i < n_tokens;
+        seq[i] = in ? p.token_seq[t0 + i] : -1, pos[i] = in ? p.token_pos[t0 + i] : 0;
+    }
 #pragma unroll
-            for (int e = 0; e < 8; e++) ss += v[e] * v[e];
+    for (int i = 0; i < PROMPT_TOKENS; i++) {
+        const bool on = seq[i] >= 0;
+        slot[i] = caching && on ? p.seq_slot[seq[i]] : 0, len_after[i] = caching && on ? p.seq_len_after[seq[i]] : 0;
+        if (on && p.cos && threadIdx.x < HD / 64) {  // the token's angles, HD / 2 float32 of each kind, into the L1
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(p.cos + (long long)pos[i] * (HD / 2) + 32 * threadIdx.x));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(p.sin + (long long)pos[i] * (HD / 2) + 32 * threadIdx.x));
+        }
+    }
 #pragma unroll
-            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);  // over the head's lanes
-            const float *w = is_q ? p.q_norm : p.k_norm;
-            if ((is_q || is_k) && w) {
-                const float scale = 1.0f / sqrtf(ss / (float)HD + p.eps);
-                const float4 w0 = __ldg((const float4 *)(w + l * 8)), w1 = __ldg((const float4 *)(w + l * 8 + 4));
-                const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    for (int i = 0; i < PROMPT_TOKENS; i++) {
+        kept[i] = -1;
+        if (caching && seq[i] >= 0 &&
+            !(p.cache.ring_pages > 0 && pos[i] + p.cache.ring_pages * p.cache.tokens_per_page <= len_after[i] - 1))
+            kept[i] = cache_offset(p.cache, cache_page(p.cache, slot[i], pos[i]), 0, p.n_kv_heads, pos[i], HD);
+    }
+    auto load_rows = [&](bool on, int i, int round, uint4 *raw) {
+        const __nv_bfloat16 *row0 = (const __nv_bfloat16 *)p.qkv + (long long)(t0 + i) * total_heads * HD + l * 8;
 #pragma unroll
-                for (int e = 0; e < 8; e++) v[e] = wv[e] * (v[e] * scale);
-            }
-            // the element HD / 2 above or below each of this lane's, from the lane that holds it
-            float other[8];
+        for (int u = 0; u < FAST_SLOTS; u++) {
+            const int head = round * ROUND + warp * HPW + sub + u * FAST_WARPS * HPW;
+            raw[u] = on && head < limit ? *(const uint4 *)(row0 + (long long)head * HD) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    pdl_wait();
+    uint4 cur[FAST_SLOTS], next[FAST_SLOTS];
+    load_rows(seq[0] >= 0, 0, 0, cur);
 #pragma unroll
-            for (int e = 0; e < 8; e++) other[e] = __shfl_xor_sync(0xffffffffu, v[e], LPH / 2);
-            uint32_t outw[4] = {in[0], in[1], in[2], in[3]};
-            if (is_q || is_k) {
-                if (p.cos) {
+    for (int i = 0; i < PROMPT_TOKENS; i++) {
+        float cs[8], sn[8];
+        if (p.cos && seq[i] >= 0) {
+            const float4 *c4 = (const float4 *)(p.cos + (long long)pos[i] * (HD / 2) + at), *s4 = (const float4 *)(p.sin + (long long)pos[i] * (HD / 2) + at);
+            const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+            cs[0] = c0.x, cs[1] = c0.y, cs[2] = c0.z, cs[3] = c0.w, cs[4] = c1.x, cs[5] = c1.y, cs[6] = c1.z, cs[7] = c1.w;
+            sn[0] = s0.x, sn[1] = s0.y, sn[2] = s0.z, sn[3] = s0.w, sn[4] = s1.x, sn[5] = s1.y, sn[6] = s1.z, sn[7] = s1.w;
+        }
+        __nv_bfloat16 *row0 = (__nv_bfloat16 *)p.qkv + (long long)(t0 + i) * total_heads * HD + l * 8;
+        for (int round = 0; round < rounds; round++) {
+            if (round + 1 < rounds) load_rows(seq[i] >= 0, i, round + 1, next);
+            else if (i + 1 < PROMPT_TOKENS) load_rows(seq[i + 1 < PROMPT_TOKENS ? i + 1 : i] >= 0, i + 1, 0, next);
+            if (seq[i] >= 0) {  // (the same for the whole CTA)
 #pragma unroll
-                    for (int e = 0; e < 8; e++) v[e] = upper ? v[e] * cs[e] + other[e] * sn[e] : v[e] * cs[e] - other[e] * sn[e];
+                for (int u = 0; u < FAST_SLOTS; u++) {
+                    const int head = round * ROUND + warp * HPW + sub + u * FAST_WARPS * HPW;
+                    if (head - sub >= limit) break;  // the whole warp is past the end (the shuffles are for whole warps)
+                    prep_head<HD>(p, cur[u], head, head < limit, l, upper, cs, sn, row0, kept[i]);
                 }
+            }
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-                    outw[e] = *(uint32_t *)&h2;
-                }
-                if (live) *(uint4 *)(row0 + (long long)head * HD) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
-            }
-            if (live && !is_q && kept_at >= 0) {
-                __nv_bfloat16 *dst = (__nv_bfloat16 *)(is_k ? p.k_pool : p.v_pool) + kept_at +
-                                     (long long)kv_head * p.cache.tokens_per_page * HD + l * 8;
-                *(uint4 *)dst = make_uint4(outw[0], outw[1], outw[2], outw[3]);
-            }
+            for (int u = 0; u < FAST_SLOTS; u++) cur[u] = next[u];
         }
     }
 }
@@ -414,6 +503,13 @@ extern "C" int abk_qkv_prep(void *qkv, int dtype, int n_tokens, int n_heads, int
          (uintptr_t)v_pool) % 16 == 0) {
         // prompts: a token's heads in one CTA; a decode step of few tokens: one round of its warps' heads to a CTA
         const int work = q_only ? n_heads : total_heads;
+        if (n_tokens > 6 * 148) {  // more one-token CTAs than are resident at a time
+            dim3 many((unsigned)((n_tokens + PROMPT_TOKENS - 1) / PROMPT_TOKENS));
+            if (head_dim == 64) abk_launch(qkv_prep_prompt_kernel<64>, many, dim3(FAST_WARPS * 32), 0, s, p, n_tokens);
+            else if (head_dim == 128) abk_launch(qkv_prep_prompt_kernel<128>, many, dim3(FAST_WARPS * 32), 0, s, p, n_tokens);
+            else abk_launch(qkv_prep_prompt_kernel<256>, many, dim3(FAST_WARPS * 32), 0, s, p, n_tokens);
+            return ABK_LAUNCH_RESULT();
+        }
         const int per_cta = n_tokens >= 64 ? work : FAST_WARPS * (256 / head_dim);
         dim3 fast((unsigned)n_tokens, (unsigned)((work + per_cta - 1) / per_cta));
         if (head_dim == 64) abk_launch(qkv_prep_fast_kernel<64>, fast, dim3(FAST_WARPS * 32), 0, s, p, per_cta);

@@ -293,6 +293,35 @@ def test_qkv_prep_and_attention(ops, dtype, hq, hkv, hd, rotary_dim, interleaved
     np.testing.assert_allclose(np.concatenate(got_b), want["b"][1], **tol)
 
 
+@pytest.mark.parametrize("hq, hkv, hd", [(6, 2, 64), (16, 8, 128), (3, 1, 256), (40, 4, 128)])
+def test_qkv_prep_of_a_long_prompt_step(ops, hq, hkv, hd):
+    """A step of more tokens than one-token CTAs fit the GPU at a time goes to the kernel that takes several tokens
+    a CTA (40 + 8 heads: more than it holds in flight per token): the rows and the cache come out bit for bit as
+    from two steps that are short enough for the one-token kernel, and as the plain formulas give them."""
+    rng = np.random.default_rng(hq + hd)
+    eps, width, lens = 1e-6, (hq + 2 * hkv) * hd, (700, 333)
+    qn, kn = [(1 + 0.3 * rng.standard_normal(hd)).astype(np.float32) for _ in range(2)]
+    cos, sin = plain.rope_table(800, hd, 1e6)
+    data = [bf(rng.standard_normal((n, width))) for n in lens]
+    args = (dev(qn), dev(kn), eps, dev(cos), dev(sin), hd, False, hd ** -0.5)
+    one, two = Harness(hq, hkv, hd, torch.bfloat16), Harness(hq, hkv, hd, torch.bfloat16)
+    slots = [(h.cache.open_slot(), h.cache.open_slot()) for h in (one, two)]
+    q1, _ = one.step(ops, [(slots[0][0], lens[0]), (slots[0][1], lens[1])], np.concatenate(data), *args)
+    q2 = np.concatenate([two.step(ops, [(slots[1][i], lens[i])], data[i], *args)[0] for i in range(2)])
+    assert np.array_equal(q1, q2)
+    kv1, kv2 = one.cache.views[0].kv, two.cache.views[0].kv
+    assert torch.equal(kv1.page_table, kv2.page_table)
+    assert torch.equal(kv1.k, kv2.k) and torch.equal(kv1.v, kv2.v) and float(kv1.k.float().abs().sum()) > 0
+    at = 0
+    for n, qkv in zip(lens, data):
+        q, k, v = plain_prep(qkv, hq, hkv, hd, qn, kn, eps, cos, sin, hd, False, 0)
+        got = q1[at:at + n]
+        np.testing.assert_allclose(got[:, :hq * hd].reshape(n, hq, hd), q, rtol=2 ** -7, atol=2 ** -8)
+        np.testing.assert_allclose(got[:, hq * hd:(hq + hkv) * hd].reshape(n, hkv, hd), k, rtol=2 ** -7, atol=2 ** -8)
+        assert np.array_equal(got[:, (hq + hkv) * hd:].reshape(n, hkv, hd), v)
+        at += n
+
+
 def test_attention_finds_one_far_key(ops):
     """Among 600 keys with scores near zero, one key 500 places back scores high: the output must be its value."""
     hq, hkv, hd, n = 2, 1, 64, 600

@@ -425,3 +425,170 @@ def test_a_toy_mixer_is_registered_built_and_stepped(tmp_path):
             for i in [i for i in live if cut[i] + k == len(seqs[i])]:
                 engine.close(slots[i])
             live = [i for i in live if cut[i] + k < len(seqs[i])]
+
+
+# ------------------------------------------------------------------ a toy feed-forward with routing, a toy position encoding
+
+@dataclass(frozen=True)
+class TopOneExpertsSpec:
+    hidden: int
+    inter: int
+    n_experts: int
+    kind: str = "toy_top_one_experts"
+
+
+class TopOneExperts:
+    """Each token goes to the expert its router scores highest; the expert's gated MLP, times the softmax
+    weight of that score. Every expert runs on every row and the router picks: a row's result depends on
+    nothing but the row."""
+
+    def __init__(self, spec):
+        self.spec = spec
+
+    def param_shapes(self):
+        s = self.spec
+        return {"router": (s.n_experts, s.hidden), "gate": (s.n_experts * s.inter, s.hidden),
+                "up": (s.n_experts * s.inter, s.hidden), "down": (s.n_experts * s.hidden, s.inter)}
+
+    def bind(self, params, ctx):
+        s = self.spec
+        f = lambda t, *shape: t.to(device=ctx.device, dtype=torch.float32).reshape(*shape)
+        self.router = f(params["router"], s.n_experts, s.hidden)
+        self.gate, self.up = f(params["gate"], s.n_experts, s.inter, s.hidden), f(params["up"], s.n_experts, s.inter, s.hidden)
+        self.down = f(params["down"], s.n_experts, s.hidden, s.inter)
+
+    def forward(self, xn, out, batch, ws):
+        n = batch.n_rows
+        x = xn[:n].float()
+        weights = torch.softmax(x @ self.router.T, dim=-1)
+        top, chosen = weights.max(dim=-1)
+        g, u = torch.einsum("td,eid->tei", x, self.gate), torch.einsum("td,eid->tei", x, self.up)
+        every = torch.einsum("tei,edi->ted", torch.nn.functional.silu(g) * u, self.down)
+        out[:n] = every[torch.arange(n, device=x.device), chosen] * top[:, None]
+        return out
+
+
+@dataclass(frozen=True)
+class SlowedRotarySpec:
+    rotary_dim: int
+    theta: float
+    slow: float
+    kind: str = "toy_slowed_rotary"
+
+
+class SlowedRotary:
+    """Rotary angles whose lower half of the frequencies turns `slow` times slower, on interleaved pairs of the
+    first rotary_dim elements of a head: another table for the same kernel."""
+
+    def __init__(self, spec):
+        self.spec, self.rotary_dim, self.interleaved = spec, spec.rotary_dim, True
+
+    def angles(self, n_positions):
+        half = self.rotary_dim // 2
+        inv = 1.0 / self.spec.theta ** (2.0 * np.arange(half) / self.rotary_dim)
+        inv[half // 2:] /= self.spec.slow
+        return (np.arange(n_positions)[:, None] * inv[None, :]).astype(np.float32)
+
+    def tables(self, n_positions, device):
+        a = self.angles(n_positions)
+        return torch.from_numpy(np.cos(a)).to(device), torch.from_numpy(np.sin(a)).to(device)
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_built_and_stepped():
+    """Nothing in the package is changed: a feed-forward that routes each token to one of three experts and a
+    position encoding with a table of its own are defined above, registered, put into layers beside the gated
+    MLP, and stepped whole, cut and one token at a time, in slots that were used before."""
+    from abacus_b200.config import (AttentionSpec, BlockSpec, GatedMLPSpec, ModelSpec, NormSpec, ScheduleEntry,
+                                    register_architecture)
+    from abacus_b200.engine import Engine
+    from abacus_b200.models import Model, ModelLayout, expected_tensors
+    from abacus_b200.parts import BLOCKS, FEED_FORWARDS, POSITIONS
+    from abacus_b200.weights import random_tensors
+    FEED_FORWARDS.register("toy_top_one_experts", TopOneExperts)
+    POSITIONS.register("toy_slowed_rotary", SlowedRotary)
+    d, vocab, hd, rot, heads, eps = 40, 83, 24, 16, 2, 1e-5
+    position = SlowedRotarySpec(rotary_dim=rot, theta=100.0, slow=4.0)
+
+    class RoutedArchitecture:
+        name = "ToyRoutedForCausalLM"
+
+        def spec(self):
+            att = AttentionSpec(hidden=d, n_heads=heads, n_kv_heads=1, head_dim=hd, scale=hd ** -0.5, qk_norm_eps=None,
+                                position=position)
+            ffns = (TopOneExpertsSpec(d, 24, 3), GatedMLPSpec(d, 56), TopOneExpertsSpec(d, 16, 3))
+            blocks = tuple(BlockSpec(NormSpec(d, eps), att, NormSpec(d, eps), ffn) for ffn in ffns)
+            return ModelSpec("ToyRoutedForCausalLM", d, vocab, blocks, tuple(ScheduleEntry(i) for i in range(3)),
+                             NormSpec(d, eps), True, 200)
+
+        def layout(self, spec):
+            layers = [{(pn, slot): f"layers.{l}.{pn}.{slot}" for pn, part in BLOCKS.build(b).parts().items()
+                       for slot in part.param_shapes()} for l, b in enumerate(spec.layers)]
+            return ModelLayout("embed", "norm", "head", layers)
+
+    arch = register_architecture(RoutedArchitecture())
+    spec = arch.spec()
+    layout = arch.layout(spec)
+    expected, _ = expected_tensors(spec, layout)
+    tensors = random_tensors(expected, seed=11, std=0.3, norm_std=0.1)
+    engine = Engine(Model(spec, layout, tensors, torch.float32, torch.device("cuda", 0)), max_tokens=64 * 4)
+    w = {k: v.float().numpy() for k, v in tensors.items()}
+
+    def rotate(x, cos, sin):  # interleaved pairs (2i, 2i+1) of the first `rot` elements of every head
+        a, b = x[..., 0:rot:2], x[..., 1:rot:2]
+        c, s = cos[:, None, :], sin[:, None, :]
+        turned = np.stack([a * c - b * s, b * c + a * s], axis=-1).reshape(*x.shape[:-1], rot)
+        return np.concatenate([turned, x[..., rot:]], axis=-1).astype(np.float32)
+
+    picks = []
+
+    def plain_routed(ids):
+        n = len(ids)
+        x = plain.embed(ids, w["embed"])
+        angle = SlowedRotary(position).angles(n)
+        cos, sin = np.cos(angle), np.sin(angle)
+        for l, block in enumerate(spec.layers):
+            p = f"layers.{l}."
+            xn = plain.rmsnorm(x, w[p + "mixer_norm.weight"], eps)
+            q = rotate(plain.linear(xn, w[p + "mixer.wq"]).reshape(n, heads, hd), cos, sin)
+            k = rotate(plain.linear(xn, w[p + "mixer.wk"]).reshape(n, 1, hd), cos, sin)
+            v = plain.linear(xn, w[p + "mixer.wv"]).reshape(n, 1, hd)
+            x = x + plain.linear(plain.attention(q, k, v).reshape(n, heads * hd), w[p + "mixer.wo"])
+            xn = plain.rmsnorm(x, w[p + "ffn_norm.weight"], eps)
+            if isinstance(block.ffn, TopOneExpertsSpec):
+                e, inter = block.ffn.n_experts, block.ffn.inter
+                scores = np.stack([plain.softmax(row) for row in plain.linear(xn, w[p + "ffn.router"])])
+                y = np.zeros_like(x)
+                for t in range(n):
+                    c = int(scores[t].argmax())
+                    picks.append(c)
+                    gate, up = w[p + "ffn.gate"].reshape(e, inter, d)[c], w[p + "ffn.up"].reshape(e, inter, d)[c]
+                    gu = np.concatenate([plain.linear(xn[t:t + 1], gate), plain.linear(xn[t:t + 1], up)], -1)
+                    y[t] = plain.linear(plain.swiglu(gu), w[p + "ffn.down"].reshape(e, d, inter)[c])[0] * scores[t, c]
+                x = x + y
+            else:
+                gu = np.concatenate([plain.linear(xn, w[p + "ffn.gate"]), plain.linear(xn, w[p + "ffn.up"])], -1)
+                x = x + plain.linear(plain.swiglu(gu), w[p + "ffn.down"])
+        return plain.linear(plain.rmsnorm(x, w["norm"], eps), w["embed"])
+
+    rng = np.random.default_rng(6)
+    seqs = [random_tokens(rng, n, vocab) for n in (26, 7, 40)]
+    want = [plain_routed(s) for s in seqs]
+    assert len(set(picks)) == 3  # every expert is somebody's
+    for round_ in range(2):  # the second round runs in slots the first has used
+        slots = [engine.open() for _ in seqs]
+        cut = [15, 7, 3]
+        got = engine.step([(sl, s[:c], list(range(c))) for sl, s, c in zip(slots, seqs, cut)]).cpu().numpy()
+        at = 0
+        for i, c in enumerate(cut):
+            assert_logits(got[at:at + c], want[i][:c], "float32", f"routed prompt {i}")
+            at += c
+        engine.close(slots[1])
+        live, k = [0, 2], 0
+        while live:
+            got = engine.step([(slots[i], [seqs[i][cut[i] + k]], [0]) for i in live]).cpu().numpy()
+            for j, i in enumerate(live):
+                assert_logits(got[j:j + 1], want[i][cut[i] + k:cut[i] + k + 1], "float32", f"routed decode {i}")
+            k += 1
+            for i in [i for i in live if cut[i] + k == len(seqs[i])]:
+                engine.close(slots[i])
+            live = [i for i in live if cut[i] + k < len(seqs[i])]
