@@ -3,6 +3,7 @@
     python -m abacus_b200.kernels.microbench gemm --m 8 --n 4096 --k 1024 [--out f32] [--iters 20]
     python -m abacus_b200.kernels.microbench decode_attention --batch 8 --context 2176 --heads 16 --kv-heads 8
     python -m abacus_b200.kernels.microbench prefill_attention --tokens 2048 --heads 16 --kv-heads 8
+    python -m abacus_b200.kernels.microbench qkv_prep --tokens 2048 --heads 16 --kv-heads 8
     python -m abacus_b200.kernels.microbench argmax --rows 8 --vocab 151936
     python -m abacus_b200.kernels.microbench add_rmsnorm --rows 8 --width 1024
 
@@ -170,6 +171,22 @@ def bench_prefill_attention(args):
             "best_us": round(best, 2), "TFLOP/s": round(flops / us / 1e6, 2)}
 
 
+def bench_qkv_prep(args):
+    """q/k norm, rotation and the cache write of the `tokens` rows of one prompt step (batch sequences)."""
+    from . import ops
+    heads, kv_heads, hd = args.heads, args.kv_heads, args.head_dim
+    cache, kv, b, qkv, out = _attention_setup(args.batch, args.tokens, heads, kv_heads, hd, args.tokens)
+    qn, kn = torch.ones(hd, device="cuda"), torch.ones(hd, device="cuda")
+    pos = torch.arange(args.tokens + 64, device="cuda", dtype=torch.float32)[:, None]
+    inv = 1.0 / (1e6 ** (torch.arange(0, hd, 2, device="cuda", dtype=torch.float32) / hd))
+    cos, sin = torch.cos(pos * inv).contiguous(), torch.sin(pos * inv).contiguous()
+    us, best = timed_graph([lambda: ops.qkv_prep(qkv, heads, kv_heads, hd, b, qn, kn, 1e-6, cos, sin, hd, False, kv)])
+    rows = args.batch * args.tokens
+    nbytes = rows * hd * 2 * (2 * (heads + kv_heads) + heads + 2 * kv_heads)  # rows read, q and k written, k and v kept
+    return {"kernel": "qkv_prep", "rows": rows, "us": round(us, 2), "best_us": round(best, 2),
+            "GB/s": round(nbytes / us / 1e3, 1)}
+
+
 def bench_argmax(args):
     from . import ops
     copies = max(2, (160 << 20) // (args.rows * args.vocab * 4) + 1)
@@ -193,7 +210,7 @@ def bench_add_rmsnorm(args):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention", "argmax", "add_rmsnorm"])
+    ap.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention", "qkv_prep", "argmax", "add_rmsnorm"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
@@ -216,10 +233,10 @@ def main(argv=None):
     ap.add_argument("--simt", action="store_true", help="decode_attention: the CUDA-core kernel")
     ap.add_argument("--with-norm", action="store_true", help="gemm: alternate with an add_rmsnorm, as a model step does")
     args = ap.parse_args(argv)
-    if args.kernel == "prefill_attention" and "--batch" not in (argv or sys.argv):
+    if args.kernel in ("prefill_attention", "qkv_prep") and "--batch" not in (argv or sys.argv):
         args.batch = 1
     fn = {"gemm": bench_gemm, "decode_attention": bench_decode_attention, "prefill_attention": bench_prefill_attention,
-          "argmax": bench_argmax, "add_rmsnorm": bench_add_rmsnorm}[args.kernel]
+          "qkv_prep": bench_qkv_prep, "argmax": bench_argmax, "add_rmsnorm": bench_add_rmsnorm}[args.kernel]
     print(json.dumps(fn(args)))
     return 0
 

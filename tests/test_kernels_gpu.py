@@ -312,6 +312,14 @@ def test_qkv_prep_of_a_long_prompt_step(ops, hq, hkv, hd):
     kv1, kv2 = one.cache.views[0].kv, two.cache.views[0].kv
     assert torch.equal(kv1.page_table, kv2.page_table)
     assert torch.equal(kv1.k, kv2.k) and torch.equal(kv1.v, kv2.v) and float(kv1.k.float().abs().sum()) > 0
+    # for an entry that reads another entry's cache only q is prepared: k and v stay as they came, nothing is kept
+    rows = sum(lens)
+    again = dev(np.concatenate(data + [np.full((3, width), 7.0, dtype=np.float32)]), torch.bfloat16)
+    before = kv1.k.clone()
+    ops.qkv_prep(again, hq, hkv, hd, one.last_batch, *args[:5], hd, False, None, q_only=True)
+    again = again[:rows].float().cpu().numpy()
+    assert np.array_equal(again[:, :hq * hd], q1[:, :hq * hd]) and np.array_equal(again[:, hq * hd:], np.concatenate(data)[:, hq * hd:])
+    assert torch.equal(kv1.k, before)
     at = 0
     for n, qkv in zip(lens, data):
         q, k, v = plain_prep(qkv, hq, hkv, hd, qn, kn, eps, cos, sin, hd, False, 0)
