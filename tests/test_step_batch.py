@@ -1,0 +1,115 @@
+"""The index arrays of a step (engine/batch.py), on the CPU: rows, padding, the tiles and the work list that the
+prefill attention kernels walk. The kernels trust these lists; what they must hold is checked here against a
+reconstruction from the sequences alone."""
+import numpy as np
+import pytest
+
+from abacus_b200.engine.batch import CTA_SLOTS, HALVED_PAIRS, PAIRED_ROWS, TILE_ROWS, WORK_INTS, Sequence, StepBatch
+
+
+def random_step(rng, n_seqs, longest):
+    seqs = []
+    for slot in rng.permutation(64)[:n_seqs]:
+        n = int(rng.integers(1, longest + 1))
+        start = int(rng.choice([0, 0, 5, 64, 700]))
+        want = sorted(set(int(w) for w in rng.integers(0, n, int(rng.integers(0, 4)))))
+        seqs.append(Sequence(int(slot), [int(t) for t in rng.integers(0, 1000, n)], start, want))
+    return seqs
+
+
+def test_rows_and_padding_of_a_step():
+    rng = np.random.default_rng(0)
+    for trial in range(20):
+        seqs = random_step(rng, int(rng.integers(1, 7)), 300)
+        rows = sum(len(s.tokens) for s in seqs)
+        b = StepBatch(rows + 9, len(seqs) + 2, sum(len(s.want) for s in seqs) + 1, "cpu").fill(seqs)
+        assert (b.n_tokens, b.n_seqs, b.n_rows) == (rows, len(seqs), rows + 9)
+        at, wanted = 0, []
+        for i, s in enumerate(seqs):
+            n = len(s.tokens)
+            assert b.tokens[at:at + n].tolist() == s.tokens and set(b.token_seq[at:at + n].tolist()) == {i}
+            assert b.token_pos[at:at + n].tolist() == list(range(s.start, s.start + n))
+            assert (int(b.seq_slot[i]), int(b.seq_start[i]), int(b.seq_pos0[i]), int(b.seq_len_after[i])) == \
+                   (s.slot, at, s.start, s.start + n)
+            wanted += [at + w for w in s.want]
+            at += n
+        assert set(b.token_seq[rows:].tolist()) == {-1}  # padding rows belong to no sequence
+        assert b.seq_start[len(seqs):].tolist() == [rows] * 3
+        assert b.logit_rows[:len(wanted)].tolist() == wanted and b.n_logit_rows == len(wanted)
+        assert b.max_position == max(s.start + len(s.tokens) - 1 for s in seqs)
+        assert b.any_continuation == any(s.start > 0 for s in seqs)
+        exact = StepBatch(rows + 9, len(seqs) + 2, len(wanted) + 1, "cpu").fill(seqs, exact=True)
+        assert exact.n_rows == rows and exact.tokens.shape[0] == rows and exact.seq_slot.shape[0] == len(seqs)
+
+
+def test_a_step_that_does_not_fit_or_wants_a_place_it_does_not_bring_is_refused():
+    b = StepBatch(10, 2, 2, "cpu")
+    with pytest.raises(ValueError):
+        b.fill([Sequence(0, [1] * 11, 0, [])])
+    with pytest.raises(ValueError):
+        b.fill([Sequence(0, [1], 0, []), Sequence(1, [1], 0, []), Sequence(2, [1], 0, [])])
+    with pytest.raises(ValueError):
+        b.fill([Sequence(0, [1, 2, 3], 0, [3])])
+
+
+def test_a_decode_step_has_no_tiles():
+    b = StepBatch(8, 8, 8, "cpu").fill([Sequence(i, [7], 100 + i, [0]) for i in range(5)])
+    assert b.is_decode and set(b.work.reshape(-1).tolist()) == {-1}
+    for r in TILE_ROWS:
+        assert set(getattr(b, f"tiles{r}").tolist()) == {-1}
+
+
+def expected_tiles(seqs, rows_per_tile):
+    return {(i, r0) for i, s in enumerate(seqs) for r0 in range(0, len(s.tokens), rows_per_tile)}
+
+
+def pages_seen(s, r0, rows_per_tile):
+    return (s.start + min(r0 + rows_per_tile, len(s.tokens)) - 1) // 64 + 1
+
+
+@pytest.mark.parametrize("heads", [1, 3, 16, 40])
+def test_tiles_and_work_list_cover_every_row_once(heads):
+    rng = np.random.default_rng(heads)
+    halved_somewhere = False
+    for trial in range(30):
+        seqs = random_step(rng, int(rng.integers(1, 6)), int(rng.choice([40, 300, 2500])))
+        if all(len(s.tokens) == 1 for s in seqs):
+            continue
+        rows = sum(len(s.tokens) for s in seqs)
+        b = StepBatch(rows + 5, len(seqs) + 1, 16, "cpu", attention_heads=heads).fill(seqs)
+        for r in TILE_ROWS:
+            tiles = b.query_tiles(r).numpy()
+            real = tiles[tiles[:, 0] >= 0]
+            assert len(real) == len(expected_tiles(seqs, r)) == len({tuple(t) for t in real.tolist()})
+            assert {tuple(t) for t in real.tolist()} == expected_tiles(seqs, r)
+            assert (tiles[len(real):] == -1).all()  # padding behind, never between
+            seen = [seqs[i].start + r0 for i, r0 in real.tolist()]
+            assert seen == sorted(seen, reverse=True)  # the tiles that see the most keys first
+        work = b.work.numpy()
+        real = work[work[:, 0] >= 0]
+        assert (work[len(real):] == -1).all() and work.shape[1] == WORK_INTS
+        first_row = np.cumsum([0] + [len(s.tokens) for s in seqs])
+        parts, lengths = {}, []
+        for seq, r0, part, row_of_seq, pos0, n_new, slot, halved_id in real.tolist():
+            s = seqs[seq]
+            assert (row_of_seq, pos0, n_new, slot) == (int(first_row[seq]), s.start, len(s.tokens), s.slot)
+            parts.setdefault((seq, r0), []).append((part, halved_id))
+            pages = pages_seen(s, r0, PAIRED_ROWS)
+            lengths.append(pages if part == 0 else (pages + 1) // 2 if part == 1 else pages // 2)
+        assert set(parts) == expected_tiles(seqs, PAIRED_ROWS)
+        assert lengths == sorted(lengths, reverse=True)  # the CTAs with the most pages first
+        ids = []
+        for (seq, r0), ps in parts.items():
+            if len(ps) == 1:
+                assert ps[0][0] == 0  # a whole tile stands once
+            else:  # a halved tile stands twice, earlier and later keys, under one id; only long tiles are halved
+                assert sorted(p for p, _ in ps) == [1, 2] and ps[0][1] == ps[1][1]
+                assert pages_seen(seqs[seq], r0, PAIRED_ROWS) >= 8
+                ids.append(ps[0][1])
+        assert sorted(ids) == list(range(len(ids))) and b.n_halved == len(ids)
+        assert len(ids) * heads <= HALVED_PAIRS  # what the kernel has scratch memory for
+        if ids:
+            halved_somewhere = True
+            # tiles are halved only into places the device would otherwise leave empty, give or take a few
+            assert len(real) * heads <= 1.05 * CTA_SLOTS + heads
+    assert halved_somewhere or heads == 40
