@@ -113,3 +113,65 @@ def test_tiles_and_work_list_cover_every_row_once(heads):
             # tiles are halved only into places the device would otherwise leave empty, give or take a few
             assert len(real) * heads <= 1.05 * CTA_SLOTS + heads
     assert halved_somewhere or heads == 40
+
+
+# ------------------------------------------------------------------ which captured graph a step goes to
+
+def test_buckets_of_captured_steps():
+    from abacus_b200.engine.graphs import ROW_BUCKETS, POSITION_STEP, prompt_bucket, row_bucket
+    assert [row_bucket(n) for n in (1, 2, 3, 8, 9, 17, 64, 65, 256)] == [1, 2, 4, 8, 16, 24, 64, 96, 256]
+    assert row_bucket(257) is None and list(ROW_BUCKETS) == sorted(ROW_BUCKETS) and POSITION_STEP % 64 == 0
+    for n in list(range(1, 300)) + [1000, 2048, 2049, 5000, 100000]:
+        b = prompt_bucket(n)
+        assert b >= n and b >= 16 and (b & (b - 1) == 0 or b % 128 == 0)
+        assert b <= max(16, 2 * n) and (n <= 128 or b - n < max(128, n // 8) + 1)  # never much padding
+        assert prompt_bucket(b) == b  # a bucket is its own bucket
+
+
+class FakeNeed:
+    def __init__(self, window):
+        self.window = window
+
+
+class FakeContext:
+    device = "cpu"
+
+
+class FakeModel:
+    ctx, attention_heads = FakeContext(), 4
+
+    def __init__(self, window=None):
+        self.window = window
+
+    def cache_needs(self):
+        return [FakeNeed(None), None, FakeNeed(self.window)]
+
+
+class FakeEngine:
+    def __init__(self, window=None):
+        self.model = FakeModel(window)
+        self.max_context = 4096
+
+
+def test_which_steps_are_captured():
+    from abacus_b200.engine.graphs import DecodeGraphs, PromptGraphs
+    prompts = [Sequence(0, [1] * 700, 0, [699]), Sequence(1, [1] * 33, 0, [32])]
+    decode = [Sequence(i, [5], 40 + i, [0]) for i in range(5)]
+    graphs = PromptGraphs(FakeEngine())
+    assert not graphs.takes(decode)  # one token each: the decode graphs' business
+    assert not graphs.takes(prompts)  # a shape seen once is not worth a capture
+    assert graphs.takes(prompts)  # the second time it is
+    same_shape = [Sequence(3, [2] * 650, 0, [0]), Sequence(4, [2] * 90, 0, [1])]
+    assert graphs.key(same_shape) == graphs.key(prompts) == (768, 2, 2)
+    other = [Sequence(3, [2] * 650, 0, [0, 1, 2]), Sequence(4, [2] * 90, 0, [1])]
+    assert graphs.key(other) == (768, 2, 4) and not graphs.takes(other)
+    assert not PromptGraphs(FakeEngine(window=24)).takes(prompts)  # a window: steps are checked on the host
+    assert not PromptGraphs(FakeEngine(window=24)).takes(prompts)
+    d = DecodeGraphs(FakeEngine())
+    assert d.takes(decode) and not d.takes(prompts)
+    assert not d.takes([Sequence(0, [5], 3, [])])  # a decode row whose logits nobody wants is not the captured shape
+    assert not d.takes([Sequence(i, [5], 3, [0]) for i in range(257)])
+    g = d.get(decode)
+    assert (g.rows, g.position_bound) == (8, 1024) and d.get(decode) is g
+    far = [Sequence(0, [5], 1024, [0])]
+    assert d.get(far).position_bound == 2048 and d.get(far).rows == 1
