@@ -239,9 +239,17 @@ def test_layers_of_the_measured_size(tmp_path):
     for turn in range(2):
         slots = [engine.open() for _ in ids]
         places = [[0, 100, n // 2, n - 1] for n in lens]
-        got = engine.step([(s, t[:n], w) for s, t, n, w in zip(slots, ids, lens, places)]).cpu().numpy()
-        for i, w in enumerate(places):
-            assert_logits(got[4 * i:4 * i + 4], want[i][w], "bfloat16", f"turn {turn} prompt {i}", noise[i])
+        got = engine.step([(s, t[:n], list(range(n))) for s, t, n in zip(slots, ids, lens)]).cpu().numpy()
+        first = 0
+        for i, (n, w) in enumerate(zip(lens, places)):
+            mine = got[first:first + n]
+            first += n
+            assert_logits(mine[w], want[i][w], "bfloat16", f"turn {turn} prompt {i}", noise[i])
+            # Every other row: a tile of rows gone wrong (a race between a CTA's warps, a page taken twice) is off by
+            # several times the rounding noise that the plain implementation itself shows on this input, and need
+            # not touch the four places above.
+            off = np.abs(mine - want[i][:n]).max(axis=1)
+            assert off.max() <= noise[i], f"turn {turn} prompt {i}: row {off.argmax()} is off by {off.max():.3g}"
         for step in range(extra):
             got = engine.step([(s, t[n + step:n + step + 1], [0]) for s, t, n in zip(slots, ids, lens)]).cpu().numpy()
             for i, n in enumerate(lens):
