@@ -5,12 +5,13 @@
     outs = lm.generate([[1, 2, 3], [4, 5]], max_new_tokens=32, temperature=0.0)
 
 Option names and meanings follow abacus's command line (src/main.c:9-23): max_new_tokens is -n,
-temperature is --temp (0 = greedy, default 0.7), seed is --seed; top_k is the 20 that
-src/main.c:41 fixes. Prompts are token-id lists, or strings when the folder has a tokenizer.json
+temperature is --temp (0 = greedy, default 0.7), seed is --seed (default: the time, src/main.c:112);
+top_k is the 20 that src/main.c:41 fixes. Prompts are token-id lists, or strings when the folder has a tokenizer.json
 (then raw=False wraps each in the chat template of src/main.c:168, as -p does, and raw=True
 does not, as --raw).
 """
 import os
+import time
 
 from .engine import Engine, load_model
 from .engine.generate import Generator
@@ -43,9 +44,12 @@ class LM:
             raise ValueError("this model folder has no tokenizer.json; give token ids")
         return self.tokenizer.encode(prompt if raw else CHAT_TEMPLATE.format(prompt))
 
-    def generate(self, prompts, max_new_tokens=512, temperature=0.7, top_k=20, seed=0, stop_tokens=None,
+    def generate(self, prompts, max_new_tokens=512, temperature=0.7, top_k=20, seed=None, stop_tokens=None,
                  batch_size=None, raw=False, return_requests=False):
-        """Returns one list of new token ids per prompt (strings instead, if the prompts were strings)."""
+        """Returns one list of new token ids per prompt (strings instead, if the prompts were strings).
+        seed None: the time, as abacus's command line does; give a seed to draw the same tokens again."""
+        if seed is None:
+            seed = int(time.time())
         as_text = bool(prompts) and isinstance(prompts[0], str)
         ids = [self.encode(p, raw) for p in prompts] if as_text else [list(p) for p in prompts]
         sampler = Sampler(self.model.ctx.device, temperature=temperature, top_k=top_k, seed=seed)

@@ -116,22 +116,43 @@ class SequenceCache:
         for g in self.groups:
             g.book.close(slot)
 
+    def pages_short(self, slot, new_length):
+        """How many pages the group that is shortest of them lacks for the slot to grow to new_length (0: it fits)."""
+        short = 0
+        for g in self.groups:
+            want = g.book.pages_for(new_length) - len(g.book.of_slot[slot])
+            short = max(short, want - g.book.pages.n_free)
+        return short
+
     def reserve(self, slot, new_length):
-        """Room for the sequence to grow to new_length tokens; page tables on the device follow."""
+        """Room for the sequence to grow to new_length tokens; page tables on the device follow. All groups
+        get their pages or none does: a refused call leaves the cache as it was."""
         if new_length > self.max_context:
             raise CacheFull(f"context is full: {new_length} tokens, the cache holds {self.max_context} per sequence")
-        taken = []
-        try:
-            for g in self.groups:
-                added = g.book.grow(slot, new_length)
-                taken.append((g, added))
-        except CacheFull:
-            raise
-        for g, added in taken:
+        short = self.pages_short(slot, new_length)
+        if short > 0:
+            raise CacheFull(f"the cache lacks {short} free pages of {TOKENS_PER_PAGE} tokens for slot {slot} to hold "
+                            f"{new_length} tokens")
+        for g in self.groups:
+            added = g.book.grow(slot, new_length)
             if added:
                 for logical, page in added:
                     g.table_host[slot, logical] = page
                 g.table[slot].copy_(g.table_host[slot])
+
+    def reserve_all(self, wanted):
+        """reserve() for several slots at once, [(slot, new_length)]: either every one gets its room or the cache
+        is left as it was (a step is refused whole, not from its third sequence on)."""
+        for slot, new_length in wanted:
+            if new_length > self.max_context:
+                raise CacheFull(f"context is full: {new_length} tokens, the cache holds {self.max_context} per sequence")
+        for g in self.groups:
+            need = sum(max(0, g.book.pages_for(n) - len(g.book.of_slot[slot])) for slot, n in wanted)
+            if need > g.book.pages.n_free:
+                raise CacheFull(f"the cache has {g.book.pages.n_free} free pages of {TOKENS_PER_PAGE} tokens; this step "
+                                f"needs {need} more")
+        for slot, new_length in wanted:
+            self.reserve(slot, new_length)
 
     def advance(self, slot, n_new):
         self.length[slot] += n_new

@@ -28,7 +28,7 @@ struct AttnDecode {
     long long q_row;
     __nv_bfloat16 *out;  // [rows, n_heads * head_dim]
     int n_heads, n_kv_heads, head_dim;
-    float scale;
+    float scale;  // score scale times log2(e): scores and references are in units of log2
     int window;
     const int *token_seq, *token_pos, *seq_slot;
     const __nv_bfloat16 *k_pool, *v_pool;
@@ -165,11 +165,17 @@ template <int EPL> __global__ void __launch_bounds__(DEC_THREADS) attn_decode_ke
                 if (kk >= skip && kk < n_keys) sc[rd] = s;
             }
         }
-        float m = warp_max(fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3])));
+        // scores are in units of log2 and the reference is the maximum rounded up to a whole number: a key's
+        // probability is then the same bits times a power of two whichever warp or chunk it falls into
+        float m = ceilf(warp_max(fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]))));
         float pr[4];
 #pragma unroll
-        for (int rd = 0; rd < 4; rd++) pr[rd] = sc[rd] == -INFINITY ? 0.0f : expf(sc[rd] - m);
+        for (int rd = 0; rd < 4; rd++) pr[rd] = sc[rd] == -INFINITY ? 0.0f : exp2f(sc[rd] - m);
         float l = warp_sum((pr[0] + pr[1]) + (pr[2] + pr[3])) * 0.25f;  // four lanes hold each key
+        // summed unrounded, multiplied with the values as bfloat16: what the tensor-core kernels do, so that a
+        // row's result does not depend on which kernel ran it beyond rounding
+#pragma unroll
+        for (int rd = 0; rd < 4; rd++) pr[rd] = __bfloat162float(__float2bfloat16_rn(pr[rd]));
 #pragma unroll
         for (int e = 0; e < EPL; e++) o[e] = 0.0f;
 #pragma unroll
@@ -201,7 +207,7 @@ template <int EPL> __global__ void __launch_bounds__(DEC_THREADS) attn_decode_ke
         float acc = 0.0f, l = 0.0f;
         for (int w = 0; w < 4; w++) {
             float mw = warp_ml[(w * group + g) * 2];
-            float f = mw == -INFINITY ? 0.0f : expf(mw - m);
+            float f = mw == -INFINITY ? 0.0f : exp2f(mw - m);
             acc = fmaf(f, warp_o[(w * group + g) * HD + d], acc);
             l = fmaf(f, warp_ml[(w * group + g) * 2 + 1], l);
         }
@@ -234,7 +240,7 @@ template <int EPL> __global__ void __launch_bounds__(DEC_THREADS) attn_decode_ke
             }
 #pragma unroll
             for (int u = 0; u < 4; u++) {
-                float w = f[u] == -INFINITY ? 0.0f : expf(f[u] - m);
+                float w = f[u] == -INFINITY ? 0.0f : exp2f(f[u] - m);
                 acc = fmaf(w, ov[u], acc), l = fmaf(w, lv[u], l);
             }
         }
@@ -269,7 +275,7 @@ extern "C" int abk_attention_decode(const void *q, long long q_row, void *out, i
     int group = n_heads / n_kv_heads;
     AttnDecode p;
     p.q = (const __nv_bfloat16 *)q, p.q_row = q_row, p.out = (__nv_bfloat16 *)out, p.n_heads = n_heads;
-    p.n_kv_heads = n_kv_heads, p.head_dim = head_dim, p.scale = scale, p.window = window, p.token_seq = token_seq;
+    p.n_kv_heads = n_kv_heads, p.head_dim = head_dim, p.scale = scale * 1.4426950408889634f, p.window = window, p.token_seq = token_seq;
     p.token_pos = token_pos, p.seq_slot = seq_slot, p.k_pool = (const __nv_bfloat16 *)k_pool;
     p.v_pool = (const __nv_bfloat16 *)v_pool;
     p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = ring_pages;

@@ -165,7 +165,9 @@ __global__ void __launch_bounds__(RING_THREADS) attn_decode_ring_kernel(const __
                     mx_hi = fmaxf(mx_hi, fmaxf(sc[nt][2], sc[nt][3]));
                 }
                 // at least one of the warp's 16 keys is visible, so the new maxima are finite
-                const float n_lo = fmaxf(m_lo, quad_max(mx_lo)), n_hi = fmaxf(m_hi, quad_max(mx_hi));
+                // The reference is a whole power of two (the maximum rounded up, in units of log2), so a key's
+                // probability rounds to the same bfloat16 whichever CTA, warp or step meets it.
+                const float n_lo = fmaxf(m_lo, ceilf(quad_max(mx_lo))), n_hi = fmaxf(m_hi, ceilf(quad_max(mx_hi)));
                 const float c_lo = exp2f(m_lo - n_lo), c_hi = exp2f(m_hi - n_hi);
                 m_lo = n_lo, m_hi = n_hi;
                 uint32_t pf[1][4];

@@ -1,6 +1,8 @@
 // Causal grouped-query attention over the paged cache, for any head size up to 256 that is a
 // multiple of 8, any number of heads and groups, with or without a window. One block per
-// (token, query head); float32 arithmetic with an online softmax over tiles of 128 keys.
+// (token, query head); float32 arithmetic with an online softmax over tiles of 128 keys (in the
+// bfloat16 instantiation the probabilities are rounded to bfloat16 for the second product, as in
+// the tensor-core kernels, and summed unrounded).
 // It serves prefill and decode alike and is the kernel every size falls back to; the float32
 // path of the model uses nothing else for attention.
 //
@@ -60,6 +62,7 @@ template <typename T> __global__ void __launch_bounds__(ATT_THREADS) attention_g
     __shared__ float p_s[ATT_THREADS];
     __shared__ long long v_off[ATT_THREADS];
     __shared__ float scratch[33];
+    constexpr bool ROUNDED_P = sizeof(T) == 2;  // bfloat16: the probabilities are a stored tensor too
     int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, hd = p.head_dim;
     int seq = p.token_seq[t];
     T *out = (T *)p.out + ((long long)t * p.n_heads + h) * hd;
@@ -92,12 +95,23 @@ template <typename T> __global__ void __launch_bounds__(ATT_THREADS) attention_g
                 k = (const T *)p.k_pool + vo;
             }
             v_off[tid] = vo;
-            s = dot_row<T>(q_s, k, hd) * p.scale;
+            s = dot_row<T>(q_s, k, hd) * (ROUNDED_P ? p.scale * 1.4426950408889634f : p.scale);
         }
-        float m_new = fmaxf(m, block_max(s, scratch));
-        float pj = valid ? expf(s - m_new) : 0.0f;
-        float corr = expf(m - m_new);  // 0 on the first tile (m = -inf)
-        p_s[tid] = pj;
+        float m_new, pj, corr;
+        if (ROUNDED_P) {
+            // in units of log2, against the maximum rounded up to a whole number: a probability is then the same
+            // bits times a power of two whatever tile it is in, and rounds to the same bfloat16 in every kernel
+            m_new = fmaxf(m, ceilf(block_max(s, scratch)));
+            pj = valid ? exp2f(s - m_new) : 0.0f;
+            corr = exp2f(m - m_new);  // 0 on the first tile (m = -inf)
+        } else {
+            m_new = fmaxf(m, block_max(s, scratch));
+            pj = valid ? expf(s - m_new) : 0.0f;
+            corr = expf(m - m_new);
+        }
+        // the probabilities of the second product are a stored tensor: bfloat16 where the model's are (the
+        // tensor-core kernels must round them, so every kernel does); the row's sum is of the unrounded ones
+        p_s[tid] = to_float(from_float<T>(pj));
         l = l * corr + block_sum(pj, scratch);  // the barrier inside also publishes p_s and v_off
         m = m_new;
         int n_valid = pos - base + 1 < ATT_THREADS ? pos - base + 1 : ATT_THREADS;

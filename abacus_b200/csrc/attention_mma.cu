@@ -126,7 +126,10 @@ __global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(const __grid_
                     mx_lo = fmaxf(mx_lo, fmaxf(sc[nt][0], sc[nt][1]));
                     mx_hi = fmaxf(mx_hi, fmaxf(sc[nt][2], sc[nt][3]));
                 }
-                const float n_lo = fmaxf(m_lo, quad_max(mx_lo)), n_hi = fmaxf(m_hi, quad_max(mx_hi));
+                // the reference of a row's exponentials is a whole power of two (the maximum rounded up, in units
+                // of log2): whatever tile a key falls into, its probability is the same bits times a power of two,
+                // so the bfloat16 it is rounded to does not depend on how the keys were tiled, split or cut
+                const float n_lo = fmaxf(m_lo, ceilf(quad_max(mx_lo))), n_hi = fmaxf(m_hi, ceilf(quad_max(mx_hi)));
                 const float ref_lo = n_lo == -INFINITY ? 0.0f : n_lo, ref_hi = n_hi == -INFINITY ? 0.0f : n_hi;
                 const float c_lo = exp2f(m_lo - ref_lo), c_hi = exp2f(m_hi - ref_hi);
                 m_lo = n_lo, m_hi = n_hi;

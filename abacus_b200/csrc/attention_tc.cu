@@ -316,7 +316,9 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __
             // inside bfloat16 and float32), so that O is rescaled on a few early steps only; the final
             // O / l does not depend on the reference. Both warps of a quarter see the same maxima and
             // the same references, so they decide alike.
-            const float cand = fmaxf(m, mx);
+            // The reference is always a whole number (a power of two as a factor): a key's probability is then the
+            // same bits times a power of two whatever reference its step had, and rounds to the same bfloat16.
+            const float cand = fmaxf(m, ceilf(mx));
             const bool move = __any_sync(0xffffffffu, cand > m + 8.0f);  // the first step: m is -inf
             const float m_new = move ? cand : m;
             const float ref = m_new == -INFINITY ? 0.0f : m_new;

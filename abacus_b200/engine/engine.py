@@ -98,8 +98,7 @@ class Engine:
                 bad = tokens[(tokens < 0) | (tokens >= self.vocab)]
                 raise StepError(f"slot {slot}: token {int(bad[0])} is outside the vocabulary of {self.vocab}")
             seqs.append(Sequence(slot, tokens, self.cache.length[slot], [int(w) for w in want]))
-        for s in seqs:
-            self.cache.reserve(s.slot, s.start + len(s.tokens))
+        self.cache.reserve_all([(s.slot, s.start + len(s.tokens)) for s in seqs])
         return seqs
 
     def step(self, entries):
@@ -131,8 +130,7 @@ class Engine:
         seqs = [Sequence(slot, _ONE_TOKEN, self.cache.length[slot], _WANT_IT) for slot in slots]
         if len(set(slots)) != len(slots) or not self.graphs.takes(seqs):
             return None
-        for s in seqs:
-            self.cache.reserve(s.slot, s.start + 1)
+        self.cache.reserve_all([(s.slot, s.start + 1) for s in seqs])
         graph = self.graphs.get(seqs)
         logits = graph.run(seqs, tokens_dev=tokens_dev)
         self.last_batch = graph.batch

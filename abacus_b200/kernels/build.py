@@ -24,7 +24,7 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 MODULES = ("elementwise", "gemm_simt", "gemm_tc", "attention_generic", "attention_decode", "attention_mma", "gemm_rows",
-           "sampling", "attention_decode_static", "attention_decode_ring", "attention_tc")
+           "sampling", "attention_decode_static", "attention_decode_ring", "attention_tc", "utility")
 
 
 # ABACUS_TRACE=1 builds every library with the launch-timeline records of csrc/common.cuh compiled in
@@ -54,19 +54,27 @@ def _nvcc():
     return None
 
 
+_build_dir_found = None
+
+
 def _build_dir():
+    """Where built libraries go: csrc/_build/ if it can be written, else a per-user folder under the system's
+    temporary directory. Decided once per process (threads that compile side by side must agree)."""
+    global _build_dir_found
+    if _build_dir_found is not None:
+        return _build_dir_found
     inside = os.path.join(CSRC, "_build")
     try:
         os.makedirs(inside, exist_ok=True)
-        probe = os.path.join(inside, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
+        fd, probe = tempfile.mkstemp(prefix=".w", dir=inside)
+        os.close(fd)
         os.remove(probe)
-        return inside
+        found = inside
     except OSError:
-        outside = os.path.join(tempfile.gettempdir(), f"abacus_b200-build-{os.getuid()}")
-        os.makedirs(outside, exist_ok=True)
-        return outside
+        found = os.path.join(tempfile.gettempdir(), f"abacus_b200-build-{os.getuid()}")
+        os.makedirs(found, exist_ok=True)
+    _build_dir_found = found
+    return found
 
 
 def _fingerprint(module):
@@ -105,7 +113,7 @@ def compile_module(module, verbose=True, extra_flags=()):
         raise KernelBuildError(f"the kernel library for {module!r} is not built and nvcc was not found "
                                "(set ABACUS_NVCC or put nvcc on PATH)")
     out = library_path(module)
-    tmp = f"{out}.{os.getpid()}.tmp"
+    tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
     cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *_module_flags(module), *extra_flags, "-I", CSRC, "-o", tmp, src]
     if verbose:
         print(f"abacus_b200: compiling {module}.cu for sm_100a ...", file=sys.stderr, flush=True)

@@ -62,6 +62,16 @@ def _check(lib, rc, what, kernels=1):
 _i, _ll, _f = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 
 
+def fill_normal(out, key, mean, amplitude, first=0):
+    """out.flat[i] = mean + amplitude * z(key, first + i), z a unit normal that depends on (key, index) alone
+    (csrc/utility.cu; weights/random_init.py holds the host twin). out float32 or bfloat16, contiguous."""
+    _need_cuda(out)
+    lib = load_module("utility")
+    assert out.is_contiguous()
+    _check(lib, lib.abk_fill_normal(_p(out), _i(_dt(out)), _ll(out.numel()), _ll(first), ctypes.c_ulonglong(key),
+                                    _f(mean), _f(amplitude), _stream()), "fill_normal")
+
+
 def embed(tokens, table, x, status):
     """x[t] = float(table[tokens[t]]) (src/model.c:290-291). tokens int32 [T], x float32 [T, d]."""
     _need_cuda(tokens, table, x, status)

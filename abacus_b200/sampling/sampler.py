@@ -3,7 +3,10 @@
 abacus samples one sequence with one xorshift64 state seeded by --seed. Here
 every request has a state of its own, `stream_seed(seed, request index)`, so
 what a request draws does not depend on which batch it runs in; request 0 uses
-`seed` itself and so draws what abacus would.
+`seed` itself and so draws what abacus would. One deviation: xorshift64 never
+leaves state 0 (every draw would take the top token), and abacus never starts
+there because its default seed is the time (src/main.c:112); here a stream whose
+state would be 0 starts from a fixed non-zero constant instead.
 """
 import torch
 
@@ -14,8 +17,8 @@ GOLDEN = 0x9E3779B97F4A7C15
 
 
 def stream_seed(seed, request_index):
-    """Initial xorshift64 state of a request."""
-    return (seed ^ (request_index * GOLDEN)) & MASK64
+    """Initial xorshift64 state of a request; never 0 (the state xorshift64 cannot leave)."""
+    return ((seed ^ (request_index * GOLDEN)) & MASK64) or GOLDEN
 
 
 def as_signed(u):

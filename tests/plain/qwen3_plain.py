@@ -19,6 +19,7 @@ import struct
 import numpy as np
 
 F32 = np.float32
+P_ROUNDED = True  # with rnd: the probabilities are a stored tensor too (see attention)
 
 
 # ----------------------------------------------------------------- file reading
@@ -119,7 +120,7 @@ def softmax(x):
     return (e / np.sum(e, dtype=F32)).astype(F32)
 
 
-def attention(q, k, v, window=None):
+def attention(q, k, v, window=None, rnd=None):
     """Causal attention of one sequence (src/model.c:197-211).
 
     q: [n, Hq, hd]; k, v: [n, Hkv, hd]. Query head h reads kv head h // (Hq/Hkv)
@@ -127,6 +128,12 @@ def attention(q, k, v, window=None):
     token i reads keys 0..i (the loop bound of src/model.c:203 is the mask).
     abacus has no window; with `window` = W token i reads keys max(0, i-W+1)..i,
     which is what config.json's sliding_window means.
+    rnd: where a reduced-precision engine stores the probabilities for the second product (tensor cores take
+    them as bfloat16). Such an engine meets a row's keys tile by tile and cannot know the row's maximum when it
+    rounds the first; so that the rounded value does not depend on the tiling, the exponentials are taken against
+    the maximum rounded up to a whole power of two: p = 2^(s log2(e) - ceil(max s log2(e))), in (1/2, 1] at the
+    maximum. p is rounded before it multiplies the values, and the row's sum is taken of the unrounded values.
+    abacus keeps everything in float32 against the maximum itself (src/model.c:183-192, 206-210): rnd=None.
     """
     n, hq, hd = q.shape
     group = hq // k.shape[1]
@@ -137,8 +144,12 @@ def attention(q, k, v, window=None):
         for h in range(hq):
             g = h // group
             scores = (k[lo:i + 1, g, :] @ q[i, h, :]).astype(F32) * scale
-            p = softmax(scores)
-            out[i, h, :] = p @ v[lo:i + 1, g, :]
+            if rnd is None:
+                out[i, h, :] = softmax(scores) @ v[lo:i + 1, g, :]
+            else:
+                t = scores * F32(1.4426950408889634)
+                e = np.exp2(t - np.ceil(np.max(t)), dtype=F32)
+                out[i, h, :] = (rnd(e) @ v[lo:i + 1, g, :]) / np.sum(e, dtype=F32)
     return out
 
 
@@ -192,7 +203,7 @@ def forward(cfg, w, tokens, rnd=None, schedule=None):
         else:
             k, v = kept[source]
         kept.append((k, v))
-        att = r(attention(q, k, v, cfg["windows"][l]).reshape(n, hq * hd))  # src/model.c:301
+        att = r(attention(q, k, v, cfg["windows"][l], rnd=rnd if P_ROUNDED else None).reshape(n, hq * hd))  # :301
         x = x + linear(att, L["wo"])  # src/model.c:302, 305
         xn = r(rmsnorm(x, L["ffn_norm"], cfg["eps"]))  # src/model.c:306
         gate_up = r(np.concatenate([linear(xn, L["w_gate"]), linear(xn, L["w_up"])], axis=-1))  # :307

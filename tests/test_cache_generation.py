@@ -91,6 +91,43 @@ def test_sequence_cache_groups_slots_and_state():
     assert full.book.pages.n_free == 10 - 6 - 1
 
 
+def test_a_refused_reserve_leaves_every_group_as_it_was():
+    """Two groups, the windowed one first; the group of all keys is the one that runs out. A refusal must not leave
+    the windowed group with pages that its table on the device never heard of, and a step that does not fit for its
+    last sequence must not keep the pages of its first."""
+    needs = [CacheNeed(2, 16, window=100), CacheNeed(2, 16)]
+    cache = SequenceCache(needs, [None, None], max_tokens=64 * 6, dtype=torch.float32, device="cpu", max_slots=4)
+    ring, full = cache.groups
+    assert ring.need.window == 100 and full.need.window is None
+    a, b = cache.open_slot(), cache.open_slot()
+    cache.reserve(a, 64 * 4)
+    before = (list(ring.book.of_slot[b]), ring.book.pages.n_free, full.book.pages.n_free)
+    with pytest.raises(CacheFull):
+        cache.reserve(b, 64 * 3)  # the full group has 2 pages left
+    assert (list(ring.book.of_slot[b]), ring.book.pages.n_free, full.book.pages.n_free) == before
+    cache.close_slot(a)
+    cache.reserve(b, 64 * 3)
+    assert ring.table[b, :len(ring.book.of_slot[b])].tolist() == ring.book.of_slot[b]
+    assert full.table[b, :3].tolist() == full.book.of_slot[b]
+    c = cache.open_slot()
+    before = (full.book.pages.n_free, ring.book.pages.n_free, len(full.book.of_slot[b]), len(full.book.of_slot[c]))
+    with pytest.raises(CacheFull):
+        cache.reserve_all([(b, 64 * 4), (c, 64 * 3)])  # b alone would fit, both do not
+    assert (full.book.pages.n_free, ring.book.pages.n_free, len(full.book.of_slot[b]), len(full.book.of_slot[c])) == before
+    cache.reserve_all([(b, 64 * 4), (c, 64 * 2)])
+    assert full.book.pages.n_free == 0
+
+
+def test_no_request_starts_its_random_stream_at_zero():
+    """xorshift64 never leaves state 0, so no (seed, request) pair may start there, seed 0 included."""
+    golden = 0x9E3779B97F4A7C15
+    assert stream_seed(0, 0) != 0
+    for i in range(1, 50):
+        assert stream_seed((i * golden) % (1 << 64), i) != 0  # the seeds that would cancel request i's offset
+        assert stream_seed(5, i) == (5 ^ (i * golden)) % (1 << 64)
+    assert stream_seed(5, 0) == 5  # request 0 draws what abacus would with --seed 5
+
+
 def test_window_ring_size():
     for window, pages in [(1, 1), (2, 2), (64, 2), (65, 2), (66, 3), (128, 3), (130, 4)]:
         cache = SequenceCache([CacheNeed(1, 16, window=window)], [None], 64 * 64, torch.float32, "cpu")

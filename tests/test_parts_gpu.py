@@ -110,7 +110,7 @@ def test_attention_part_and_block(dname, dtype):
     k = r(plain.linear(xn, m["wk"])).reshape(n, hkv, hd)
     v = r(plain.linear(xn, m["wv"])).reshape(n, hkv, hd)
     q, k = r(plain.rope(plain.rmsnorm(q, m["q_norm"], eps), cos, sin)), r(plain.rope(plain.rmsnorm(k, m["k_norm"], eps), cos, sin))
-    att = r(plain.attention(q, k, v).reshape(n, hq * hd))
+    att = r(plain.attention(q, k, v, rnd=plain.bf16_round if dtype == torch.bfloat16 else None).reshape(n, hq * hd))
     mix = plain.linear(att, m["wo"])
     x1 = x0 + mix
     xn2 = r(plain.rmsnorm(x1, w["ffn_norm"]["weight"], eps))

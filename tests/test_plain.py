@@ -4,6 +4,7 @@ import json
 import os
 
 import numpy as np
+import pytest
 
 from helpers import TINY, log_softmax64, make_model_folder
 from plain import qwen3_plain as plain
@@ -11,22 +12,33 @@ from plain import qwen3_plain as plain
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
-def test_plain_matches_abacus_engine(tmp_path):
-    """abacus's engine is int8 (tests/golden/make_golden.py), so its own rule for quantised weights
-    applies (tools/check.py:24, 94-97): the same top token at >= 90 % of the positions and a mean KL
-    <= 0.02. (Seen here: 100 %, KL 8.6e-4, mean abs difference 0.03 on logits of std 1.3.)"""
-    meta = json.load(open(os.path.join(GOLDEN, "tinyA_abacus.json")))
-    golden = np.load(os.path.join(GOLDEN, "tinyA_abacus.npy"))
-    folder = make_model_folder(tmp_path, "A")
+@pytest.mark.parametrize("name", ["A", "B392"])
+def test_plain_matches_abacus_engine(tmp_path, name):
+    """abacus's engine is int8 (tests/golden/make_golden.py), so the comparison is statistical, in the manner of
+    its own rule for quantised weights (tools/check.py:24, 94-97: the same top token at >= 90 % of the positions,
+    mean KL <= 0.02) but tighter, so that a slip in one formula shows: abacus's top token is the plain model's or within 0.1 of it at
+    every position, the mean KL is <= 0.01 (seen: 1.0e-3 and 7.0e-3; abacus's own bound is 0.02), and the mean
+    absolute difference is <= 8 % of the logits' standard deviation (seen: 2.4 % and 5.5 %). Tried against slips:
+    a rotation base twice as large, q and k norm weights swapped, and query head h reading kv head h % n_kv all
+    fail these bounds on B392 (KL 0.07 to 1.4). B392 is configuration B (untied
+    head, groups of 3, head size decoupled from the width, eps 1e-5, norm weights off 1) with the vocabulary
+    padded to what the int8 engine loads."""
+    meta = json.load(open(os.path.join(GOLDEN, f"tiny{name}_abacus.json")))
+    golden = np.load(os.path.join(GOLDEN, f"tiny{name}_abacus.npy"))
+    folder = make_model_folder(tmp_path, name)
     digest = hashlib.sha256(open(os.path.join(folder, "model.safetensors"), "rb").read()).hexdigest()
     assert digest == meta["weights_sha256"], "the random weights are not the ones the golden logits were made with"
     cfg, w = plain.load(folder)
     got = plain.forward(cfg, w, meta["ids"])
     assert got.shape == golden.shape
-    agreement = (got.argmax(-1) == golden.argmax(-1)).mean()
     lp, lq = log_softmax64(got), log_softmax64(golden)
     kl = (np.exp(lp) * (lp - lq)).sum(-1).mean()
-    assert agreement >= 0.90 and kl <= 0.02, (agreement, kl)
+    # abacus's top token must be the plain model's top token or within a tenth of it (int8 noise flips near-ties:
+    # every disagreement seen had a margin below 0.09 on logits of standard deviation 1.3 to 1.6)
+    behind = got.max(-1) - got[np.arange(len(got)), golden.argmax(-1)]
+    mean_diff = np.abs(got - golden).mean() / got.std()
+    print(name, "kl", kl, "behind", behind.max(), "mean difference / std", mean_diff)
+    assert behind.max() <= 0.1 and kl <= 0.01 and mean_diff <= 0.08, (behind.max(), kl, mean_diff)
 
 
 def test_causality_and_prefix_invariance(tmp_path):
@@ -98,7 +110,7 @@ def test_sampler_follows_abacus():
         seen.add(tok)
     assert len(seen) > 5
     assert plain.xorshift64(1) == 1082269761  # 1 ^ 1<<13 = 8193; ^ >>7 = 8257; ^ <<17
-    assert plain.sample(big, 0.8, 0)[0] == int(np.argmax(big))  # a zero state stays zero: r = 0 takes the top
+    assert plain.xorshift64(0) == 0  # the one state the generator cannot leave; the library never starts a stream there
 
 
 def test_bf16_round_matches_export():
