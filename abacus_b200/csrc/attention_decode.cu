@@ -286,15 +286,11 @@ extern "C" int abk_attention_decode(const void *q, long long q_row, void *out, i
     if (smem > 200 * 1024) ABK_REFUSE("attention_decode: a group of %d query heads needs %zu bytes of shared memory", group, smem);
     dim3 grid(max_chunks, n_kv_heads, n_rows);
     cudaStream_t s = (cudaStream_t)stream;
-    static bool configured = false;
-    if (!configured) {  // once, and not inside a stream capture
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(attn_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(attn_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    {   // once per device, and not inside a stream capture
+        cudaError_t e = abk_allow_shared_memory((const void *)attn_decode_kernel<2>, 200 * 1024);
+        if (e == cudaSuccess) e = abk_allow_shared_memory((const void *)attn_decode_kernel<4>, 200 * 1024);
+        if (e == cudaSuccess) e = abk_allow_shared_memory((const void *)attn_decode_kernel<8>, 200 * 1024);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     if (head_dim == 64) attn_decode_kernel<2><<<grid, DEC_THREADS, smem, s>>>(p);
     else if (head_dim == 128) attn_decode_kernel<4><<<grid, DEC_THREADS, smem, s>>>(p);

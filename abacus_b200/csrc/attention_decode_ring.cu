@@ -305,13 +305,10 @@ extern "C" int abk_attention_decode_ring(const void *q, long long q_row, void *o
     p.token_seq = token_seq, p.token_pos = token_pos, p.seq_slot = seq_slot;
     p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = ring_pages;
     p.cache.tokens_per_page = tokens_per_page;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_ring_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(attn_decode_ring_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    {   // once per device
+        cudaError_t e = abk_allow_shared_memory((const void *)attn_decode_ring_kernel<64>, 224 * 1024);
+        if (e == cudaSuccess) e = abk_allow_shared_memory((const void *)attn_decode_ring_kernel<128>, 224 * 1024);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     // CTAs per (row, kv head): as many as a cluster holds (8) and the pages allow, as long as all of the grid's
     // clusters are on the device at once; a grid so small that they still are with a ring twice as deep

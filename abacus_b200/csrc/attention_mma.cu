@@ -190,13 +190,10 @@ extern "C" int abk_attention_prefill(const void *qkv, long long row_width, int n
     p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = 0;
     p.cache.tokens_per_page = tokens_per_page;
     const int smem = (1 + 2 * PRE_STAGES) * PAGE * head_dim * 2 + 1024 + 128;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
+    {   // once per device
+        cudaError_t e = abk_allow_shared_memory((const void *)attn_prefill_kernel<64>, 120 * 1024);
+        if (e == cudaSuccess) e = abk_allow_shared_memory((const void *)attn_prefill_kernel<128>, 120 * 1024);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     dim3 grid(n_tiles, n_heads);
     cudaStream_t s = (cudaStream_t)stream;

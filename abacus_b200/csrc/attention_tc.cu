@@ -522,12 +522,7 @@ extern "C" int abk_attention_prefill_tc(const void *qkv, long long row_width, in
     p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = 0;
     p.cache.tokens_per_page = tokens_per_page;
     const int smem = Q_BYTES + 2 * KV_STAGES * KV_BYTES + P_BYTES + 1024;  // 113 KB: two CTAs to an SM, to the byte
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    if (cudaError_t e = abk_allow_shared_memory((const void *)attn_prefill_tc_kernel, smem)) return (int)e;  // once per device
     abk_launch(attn_prefill_tc_kernel, dim3((unsigned)(n_work * n_heads)), dim3(FA_THREADS), smem, (cudaStream_t)stream, qm, km,
                vm, p);
     return ABK_LAUNCH_RESULT();

@@ -81,7 +81,39 @@ __device__ __forceinline__ void pdl_wait() {
 
 #ifdef __CUDACC__
 #include <cstdlib>
+#include <mutex>
+#include <map>
 #include <utility>
+// Lets `kernel` use `bytes` of dynamic shared memory (more than the 48 KB a kernel gets unasked). The setting is per
+// device and per kernel: it is made when a pair first asks, and again when it asks for more than it has; other
+// calls cost a lookup under a lock.
+static inline cudaError_t abk_allow_shared_memory(const void *kernel, int bytes) {
+    static std::mutex lock;
+    static std::map<std::pair<int, const void *>, int> allowed;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> guard(lock);
+    auto it = allowed.find({device, kernel});
+    if (it != allowed.end() && it->second >= bytes) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) allowed[{device, kernel}] = bytes;
+    return e;
+}
+// SMs of the current device (148 on a B200), asked once per device.
+static inline int abk_sm_count() {
+    static std::mutex lock;
+    static int of_device[64];
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+    std::lock_guard<std::mutex> guard(lock);
+    if (!of_device[device]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+        of_device[device] = n;
+    }
+    return of_device[device];
+}
 static inline bool abk_pdl_enabled() {
     static int on = -1;
     if (on < 0) {

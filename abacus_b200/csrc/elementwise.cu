@@ -184,14 +184,14 @@ extern "C" int abk_swiglu(const void *gate_up, void *act, int dtype, int n_token
     if (block <= 0 || inter % block) ABK_REFUSE("swiglu: turns of %d columns do not divide %d", block, inter);
     if (dtype == ABK_BF16 && inter % 8 == 0 && block % 8 == 0 && ((uintptr_t)gate_up | (uintptr_t)act) % 16 == 0) {
         long long groups = total >> 3, want = (groups + 255) / 256;
-        int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+        int blocks = (int)(want > abk_sm_count() * 16 ? abk_sm_count() * 16 : want);
         abk_launch(swiglu_bf16x8_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16 *)gate_up,
                    (__nv_bfloat16 *)act, groups, inter, block);
         return ABK_LAUNCH_RESULT();
     }
     int threads = 256;
     long long blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks > abk_sm_count() * 32) blocks = abk_sm_count() * 32;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == ABK_BF16)
         abk_launch(swiglu_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, (const __nv_bfloat16 *)gate_up, (__nv_bfloat16 *)act, total, inter, block);
@@ -503,7 +503,7 @@ extern "C" int abk_qkv_prep(void *qkv, int dtype, int n_tokens, int n_heads, int
          (uintptr_t)v_pool) % 16 == 0) {
         // prompts: a token's heads in one CTA; a decode step of few tokens: one round of its warps' heads to a CTA
         const int work = q_only ? n_heads : total_heads;
-        if (n_tokens > 6 * 148) {  // more one-token CTAs than are resident at a time
+        if (n_tokens > 6 * abk_sm_count()) {  // more one-token CTAs than are resident at a time
             dim3 many((unsigned)((n_tokens + PROMPT_TOKENS - 1) / PROMPT_TOKENS));
             if (head_dim == 64) abk_launch(qkv_prep_prompt_kernel<64>, many, dim3(FAST_WARPS * 32), 0, s, p, n_tokens);
             else if (head_dim == 128) abk_launch(qkv_prep_prompt_kernel<128>, many, dim3(FAST_WARPS * 32), 0, s, p, n_tokens);

@@ -169,13 +169,13 @@ extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dt
     if (M > 64) ABK_REFUSE("gemm_rows: %d rows are more than 64", M);
     if (K <= 0 || K % 32 || ldx % 8 || ldw % 8) ABK_REFUSE("gemm_rows: K = %d must be a multiple of 32 and the pitches of 8", K);
     if (((uintptr_t)x | (uintptr_t)w) & 15) ABK_REFUSE("gemm_rows: operands must be 16-byte aligned");
-    const bool narrow = (N + 15) / 16 < 2 * 148;  // too few tiles of 16 for two CTAs on every SM
+    const bool narrow = (N + 15) / 16 < 2 * abk_sm_count();  // too few tiles of 16 for two CTAs on every SM
     const int tiles = narrow ? (N + 7) / 8 : (N + 15) / 16;
     // a long K over few tiles: clusters that split K, one turn of loads to a CTA, while the grid stays small
     const int turn = 32 * ROWS_WARPS * (M <= 16 ? 4 : 2);
     int ranks = narrow ? K / turn : 1;
     if (ranks > 8) ranks = 8;
-    while (ranks > 1 && ((K / 32) % ranks || (long long)tiles * ranks > 8 * 148)) ranks--;
+    while (ranks > 1 && ((K / 32) % ranks || (long long)tiles * ranks > 8 * abk_sm_count())) ranks--;
     if (ranks < 1) ranks = 1;
     dim3 grid(tiles * ranks);
     cudaStream_t s = (cudaStream_t)stream;

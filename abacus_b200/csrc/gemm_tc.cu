@@ -492,13 +492,8 @@ static int tensor_map(const void *ptr, long long rows, long long cols, long long
 template <int BN, int STAGES, typename TO>
 static int launch(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g, dim3 grid, cudaStream_t s) {
     auto kernel = gemm_tc_kernel<BN, STAGES, TO>;
-    static bool configured = false;
     constexpr int bytes = GemmSmem<BN, STAGES>::BYTES;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    if (cudaError_t e = abk_allow_shared_memory((const void *)kernel, bytes)) return (int)e;  // once per device
     abk_launch_clusters(kernel, grid, dim3(GEMM_THREADS), (size_t)bytes, s, dim3(1, 1, g.in_cluster ? g.splits : 1), mp, mq, g);
     return ABK_LAUNCH_RESULT();
 }
@@ -507,14 +502,9 @@ template <int BN, int STAGES, typename TO>
 static int launch_persistent(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g, int m_tiles, int tiles,
                              cudaStream_t s) {
     auto kernel = gemm_tc_persistent_kernel<BN, STAGES, TO>;
-    static bool configured = false;
     constexpr int bytes = GemmSmem<BN, STAGES>::BYTES;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    abk_launch(kernel, dim3(tiles < 148 ? tiles : 148), dim3(GEMM_THREADS), (size_t)bytes, s, mp, mq, g, m_tiles, tiles);
+    if (cudaError_t e = abk_allow_shared_memory((const void *)kernel, bytes)) return (int)e;  // once per device
+    abk_launch(kernel, dim3(tiles < abk_sm_count() ? tiles : abk_sm_count()), dim3(GEMM_THREADS), (size_t)bytes, s, mp, mq, g, m_tiles, tiles);
     return ABK_LAUNCH_RESULT();
 }
 
@@ -536,14 +526,9 @@ extern "C" int abk_gemm_tc_swiglu(const void *x, const void *w, void *act, int M
     g.partials = nullptr, g.tickets = nullptr, g.status = status, g.vec = 1, g.in_cluster = 0, g.weights_are_p = 0;
     const int m_tiles = (M + TILE_P - 1) / TILE_P, tiles = m_tiles * (N / 128);
     auto kernel = gemm_tc_persistent_kernel<256, 4, __nv_bfloat16, true>;
-    static bool configured = false;
     constexpr int bytes = GemmSmem<256, 4>::BYTES;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    abk_launch(kernel, dim3(tiles < 148 ? tiles : 148), dim3(GEMM_THREADS), (size_t)bytes, (cudaStream_t)stream, mx, mw, g,
+    if (cudaError_t e = abk_allow_shared_memory((const void *)kernel, bytes)) return (int)e;  // once per device
+    abk_launch(kernel, dim3(tiles < abk_sm_count() ? tiles : abk_sm_count()), dim3(GEMM_THREADS), (size_t)bytes, (cudaStream_t)stream, mx, mw, g,
                m_tiles, tiles);
     return ABK_LAUNCH_RESULT();
 }
@@ -581,7 +566,7 @@ extern "C" int abk_gemm_tc(const void *x, const void *w, void *out, int out_dtyp
         bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     } else {  // columns are output features
         long long tiles256 = (long long)((M + TILE_P - 1) / TILE_P) * ((N + 255) / 256);
-        bn = N > 128 && tiles256 >= 148 ? 256 : N > 64 ? 128 : 64;
+        bn = N > 128 && tiles256 >= abk_sm_count() ? 256 : N > 64 ? 128 : 64;
     }
     if (force_bn) bn = force_bn;
     // many rows: the persistent kernel, column tiles of 256 if that still gives most SMs a tile, else of 128
@@ -598,7 +583,19 @@ extern "C" int abk_gemm_tc(const void *x, const void *w, void *out, int out_dtyp
     int k_blocks = (K + TILE_K - 1) / TILE_K;
     long long tiles = (long long)grid.x * grid.y;
     int splits = 1;
-    if (tiles <= 32) {
+    if (swap) {
+        // A decode step: the weights are the lanes and stream through once, so what counts is that every SM has
+        // weights in flight all the time. K is shared out until some 180 CTAs work (a power of two of splits, never
+        // fewer than 4 blocks of 64 columns each). Measured at 16 rows, splits 1 / 2 / 4 / 8: 6144 x 2560 (48 tiles)
+        // 15.7 / 11.9 / 10.6 / 11.1 us; 2560 x 9728 (20 tiles) 49 / 28 / 17.3 / 14.7 us; 6144 x 4096 (48 tiles)
+        // 23.7 / 16.4 / 14.6 / 13.9 us; 19456 x 2560 (152 tiles) 23.0 / 23.2 / 26.9 / 36.9 us. With more than 32
+        // columns (tokens) a partial tile costs more to add up, and beyond four splits that outweighs the gain
+        // (2560 x 4096 at 64 rows: 23.7 / 16.9 / 12.3 / 15.3 us) unless the tiles are very few.
+        const int want = (int)((180 + tiles / 2) / tiles);
+        const int most = bn <= 32 || tiles <= 8 ? 8 : 4;
+        for (splits = 1; splits * 2 <= want && splits * 2 <= most && k_blocks / (splits * 2) >= 4;) splits *= 2;
+        if (want >= 3 && splits == 2 && most >= 4 && k_blocks / 4 >= 4) splits = 4;  // (3 rounds up: 48 tiles take four)
+    } else if (tiles <= 32) {
         // Few tiles: share them along K, but sparingly: every split pays for its partial tile and for adding them
         // up. Measured at 64 rows with the splits as a cluster: 8 tiles (1024 x 2048) 14.3 us unsplit, 8.5 with four;
         // 32 tiles (4096 x 1024) 9.6 us unsplit, 8.6 with four; 48 tiles (6144 x 1024) 9.9 us unsplit, 12.0 with four.

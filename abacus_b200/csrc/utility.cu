@@ -51,7 +51,7 @@ extern "C" int abk_fill_normal(void *out, int dtype, long long n, long long firs
     if (dtype != ABK_F32 && dtype != ABK_BF16) ABK_REFUSE("fill_normal: dtype %d is neither float32 nor bfloat16", dtype);
     const int threads = 256;
     const long long blocks = (n + threads - 1) / threads;
-    const int grid = (int)(blocks < 148 * 16 ? blocks : 148 * 16);
+    const int grid = (int)(blocks < abk_sm_count() * 16 ? blocks : abk_sm_count() * 16);
     if (dtype == ABK_F32)
         fill_normal_kernel<float><<<grid, threads, 0, (cudaStream_t)stream>>>((float *)out, n, first, key, mean, amplitude);
     else

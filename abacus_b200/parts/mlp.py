@@ -8,7 +8,7 @@ import torch
 
 from ..kernels import ops
 from .base import FEED_FORWARDS, to_device
-from .linear import ROWS_KERNEL_UP_TO, Linear
+from .linear import Linear, rows_kernel_wins
 
 
 @FEED_FORWARDS.register("gated_mlp")
@@ -39,7 +39,7 @@ class GatedMLP:
         n, inter = batch.n_rows, self.spec.inter
         act = ws.get("act", (n, inter), self.ctx.dtype)
         w = self.gate_up.weight
-        if n <= ROWS_KERNEL_UP_TO and ops.gemm_rows_takes(xn, w, act, n):
+        if rows_kernel_wins(n, w, gated=True) and ops.gemm_rows_takes(xn, w, act, n):
             ops.gemm_rows_swiglu(xn, w, act, n, self.block)  # a handful of rows: product and activation in one
         elif ops.gemm_tc_swiglu_takes(xn, w, act, n, self.block):
             ops.gemm_tc_swiglu(xn, w, act, n)  # a prompt: the activation in the product's epilogue
