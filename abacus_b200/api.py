@@ -45,16 +45,17 @@ class LM:
         return self.tokenizer.encode(prompt if raw else CHAT_TEMPLATE.format(prompt))
 
     def generate(self, prompts, max_new_tokens=512, temperature=0.7, top_k=20, seed=None, stop_tokens=None,
-                 batch_size=None, raw=False, return_requests=False):
+                 batch_size=None, raw=False, return_requests=False, on_token=None):
         """Returns one list of new token ids per prompt (strings instead, if the prompts were strings).
-        seed None: the time, as abacus's command line does; give a seed to draw the same tokens again."""
+        seed None: the time, as abacus's command line does; give a seed to draw the same tokens again.
+        on_token(request, token) is called for every kept token as soon as the host has it."""
         if seed is None:
             seed = int(time.time())
         as_text = bool(prompts) and isinstance(prompts[0], str)
         ids = [self.encode(p, raw) for p in prompts] if as_text else [list(p) for p in prompts]
         sampler = Sampler(self.model.ctx.device, temperature=temperature, top_k=top_k, seed=seed)
         stops = self.stop_tokens() if stop_tokens is None else list(stop_tokens)
-        gen = Generator(self.engine, sampler, stops)
+        gen = Generator(self.engine, sampler, stops, on_token=on_token)
         requests = gen.generate(ids, max_new_tokens, batch_size=batch_size)
         self.last_stats = gen.stats
         if return_requests:

@@ -185,12 +185,22 @@ def main(argv=None):
             sys.stderr.write("abacus: this model folder has no tokenizer.json; use --ids\n")
             return 1
         ids = lm.encode(o.prompt, raw=o.raw)
+        out = sys.stdout.buffer if hasattr(sys.stdout, "buffer") else None
+
+        def show(request, token):  # each piece as it comes, special tokens left out (src/main.c:177-180)
+            if not lm.tokenizer.is_special(token):
+                piece = lm.tokenizer.pieces[token] if 0 <= token < len(lm.tokenizer.pieces) else b""
+                if out is not None:
+                    out.write(piece)
+                    out.flush()
+                else:
+                    sys.stdout.write(piece.decode("utf-8", errors="replace"))
+                    sys.stdout.flush()
+
         t0 = time.perf_counter()
         req = lm.generate([ids], max_new_tokens=o.steps, temperature=o.temp, top_k=o.top_k, seed=o.seed,
-                          return_requests=True)[0]
+                          return_requests=True, on_token=show)[0]
         t1 = time.perf_counter()
-        sys.stdout.write(lm.tokenizer.decode(req.output))
-        sys.stdout.flush()
         first = lm.last_stats.get("t_first_token", t1) - t0
         rest = max(t1 - t0 - first, 1e-9)
         sys.stderr.write(f"\n\nprompt {len(ids)} tokens, {len(ids) / max(first, 1e-9):.1f} tok/s | "

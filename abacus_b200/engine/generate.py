@@ -106,8 +106,10 @@ class Generator:
     """Runs requests through an engine. `engine` needs open(), close(slot), step(entries) -> logits,
     max_context and a cache with n_pages and max_slots; `sampler` needs states() and sample()."""
 
-    def __init__(self, engine, sampler, stop_tokens=()):
-        self.engine, self.sampler, self.stop_tokens = engine, sampler, tuple(stop_tokens)
+    def __init__(self, engine, sampler, stop_tokens=(), on_token=None):
+        """on_token(request, token): called for every token a request keeps, as soon as the host has it (the chat
+        loop prints each piece as it comes, src/main.c:177-180)."""
+        self.engine, self.sampler, self.stop_tokens, self.on_token = engine, sampler, tuple(stop_tokens), on_token
         self.stats = {"prefill_steps": 0, "decode_steps": 0, "batches": 0}
         self.rng = None
 
@@ -182,7 +184,12 @@ class Generator:
                 now = time.perf_counter()  # the tokens are on the host
                 self.stats.setdefault("t_first_token", now)
                 self.stats["t_end"] = now
+                kept = [len(r.output) for r in rows]
                 finished, entries = live.take(sampled)
+                if self.on_token is not None:
+                    for r, n in zip(rows, kept):
+                        for token in r.output[n:]:
+                            self.on_token(r, token)
                 for r in finished:
                     engine.close(r.slot)
                     r.slot = -1

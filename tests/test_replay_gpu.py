@@ -40,7 +40,7 @@ class Case:
             self.requests[f"first{i}"] = random_tokens(rng, i, self.vocab)
         self.rnd = plain.bf16_round if dtype == "bfloat16" else None
         self.dtype = dtype
-        self._want, self._noise = {}, {}
+        self._want, self._noise, self.whole = {}, {}, {}
 
     def want(self, rid):
         if rid not in self._want:
@@ -59,6 +59,15 @@ class Case:
 
     def check(self, got, rid, rows, what):
         assert_logits(got, self.want(rid)[rows], self.dtype, f"{what} of {rid}", noise=self.noise(rid))
+        # In float32 every reduction's order depends on the element's own place alone, so however the work is cut
+        # and whatever else is in the batch, a position's logits are the same bits (abacus's own whole-sequence,
+        # five-token and one-by-one runs are bit-identical too; tools/check.py:70-75 runs both cuts for this).
+        if self.dtype == "float32":
+            if rid not in self.whole:
+                assert rows == slice(0, len(self.requests[rid])), "the whole request comes first"
+                self.whole[rid] = np.array(got)
+            else:
+                assert np.array_equal(got, self.whole[rid][rows]), f"{what} of {rid}: not the bits of the whole request"
 
 
 @pytest.fixture(scope="module")
@@ -112,8 +121,11 @@ def test_replay(folders, tmp_path, name, dtype):
                                f"{name} batch {b} decode {k}")
                 live = [rid for rid in live if rid not in ends]
                 k += 1
-        # 4. long decode, one token at a time after a 40-token prompt
+        # 4. long decode, one token at a time after a 40-token prompt (whole first, for the comparison of cuts)
         toks, n = R["long"], len(R["long"])
+        for rid in ["long", "first1", "first2", "first3"]:
+            m = len(R[rid])
+            case.check(run.step([(rid, R[rid], list(range(m)))], end=[rid]).reshape(m, V), rid, slice(0, m), f"{name} whole")
         rows = [run.step([("long", toks[:40], [39])]).reshape(1, V)]
         for i in range(40, n):
             rows.append(run.step([("long", [toks[i]], [0])], end=["long"] if i == n - 1 else []).reshape(1, V))

@@ -1,0 +1,154 @@
+"""Schedules of steps that the replay tests do not reach, each against the plain implementation: the command
+line's text path, a decode that crosses the bound its captured graph was made for, a step that mixes a sequence
+bringing many tokens with sequences bringing one, more one-token sequences than the largest captured step
+holds, and sequences that go on by several tokens at once."""
+import json
+import os
+import shutil
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from helpers import ROOT, SHARP, TINY, assert_logits, random_tokens
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def folder_of(tmp_path, name, **changes):
+    """A model folder of tiny configuration `name` with some keys of its config.json changed."""
+    from abacus_b200.config import Qwen3Config
+    from abacus_b200.weights import write_random_model
+    t = TINY[name]
+    raw = dict(t["cfg"], architectures=["Qwen3ForCausalLM"], model_type="qwen3", **changes)
+    return write_random_model(os.path.join(str(tmp_path), "m"), Qwen3Config.from_dict(raw), seed=t["seed"],
+                              norm_std=t["norm_std"], scales=SHARP)
+
+
+def test_command_line_text_tokenize_and_bench(tmp_path):
+    """`abacus FOLDER -p TEXT`: chat template, tokenizer, generation, pieces printed as they come, special tokens left
+    out, the speed line on stderr (src/main.c:165-186); --raw; --tokenize (src/main.c:146-149); --bench (src/main.c:65-82).
+    The folder has the synthetic tokenizer of tests/golden/ and a model whose vocabulary holds its ids."""
+    from abacus_b200.api import CHAT_TEMPLATE
+    from abacus_b200.tokenizer import Tokenizer
+    folder = folder_of(tmp_path, "A", vocab_size=460, eos_token_id=459)
+    shutil.copy(os.path.join(GOLDEN, "tokenizer_synthetic.json"), os.path.join(folder, "tokenizer.json"))
+    tok = Tokenizer.from_file(os.path.join(folder, "tokenizer.json"))
+    cfg, w = plain.load(folder)
+    stops = sorted(set(tok.stop_ids()) | {459})
+    exe = [sys.executable, os.path.join(ROOT, "bin", "abacus"), folder, "--fp32"]
+
+    def run(*args):
+        done = subprocess.run([*exe, *args], check=True, capture_output=True)
+        return done.stdout.decode("utf-8", errors="replace"), done.stderr.decode()
+
+    text = "Why is the sea salty?"
+    for raw in (False, True):
+        ids = tok.encode(text if raw else CHAT_TEMPLATE.format(text))
+        want = plain.generate(cfg, w, ids, 12, stop=stops)
+        out, err = run("-p", text, "--temp", "0", "-n", "12", *(["--raw"] if raw else []))
+        assert out == tok.decode(want), (raw, out, want)
+        assert f"prompt {len(ids)} tokens, " in err and f"| generated {len(want)} tokens, " in err and "tok/s" in err
+    # sampled: the same seed draws the same text, and what request 0 draws is what abacus's loop would (src/main.c:52)
+    ids = tok.encode(CHAT_TEMPLATE.format(text))
+    want = plain.generate(cfg, w, ids, 10, temp=0.9, seed=11, stop=stops)
+    assert run("-p", text, "--temp", "0.9", "--seed", "11", "-n", "10")[0] == tok.decode(want)
+    out, _ = run("--tokenize", "It's 2026, and the engine writes <|im_end|> tokens.")
+    assert [int(t) for t in out.split()] == tok.encode("It's 2026, and the engine writes <|im_end|> tokens.")
+    res = json.loads(run("--bench", "64", "8", "--batch", "3")[0])
+    assert res["pp"] == 64 and res["tg"] == 8 and res["batch"] == 3 and res["prefill_tok_s"] > 0 and res["decode_tok_s"] > 0
+
+
+@pytest.mark.parametrize("name, dtype", [("A", "float32"), ("D", "bfloat16")])
+def test_decode_across_the_bound_of_a_captured_graph(tmp_path, name, dtype):
+    """A decode graph is captured for positions below a bound that goes in steps of 1,024. A sequence that decodes
+    from position 1,015 to 1,035 leaves one graph and enters the next in the middle of a request."""
+    from abacus_b200.engine import Engine, load_model
+    from abacus_b200.engine.graphs import POSITION_STEP
+    folder = folder_of(tmp_path, name, max_position_embeddings=1152)
+    cfg, w = plain.load(folder)
+    rng = np.random.default_rng(5)
+    first, last = POSITION_STEP - 9, POSITION_STEP + 11
+    ids = [random_tokens(rng, last + 1, cfg["vocab"]), random_tokens(rng, last + 1 - 400, cfg["vocab"])]
+    rnd = plain.bf16_round if dtype == "bfloat16" else None
+    exact = [plain.forward(cfg, w, t) for t in ids]
+    want = [plain.forward(cfg, w, t, rnd=rnd) if rnd else e for t, e in zip(ids, exact)]
+    noise = [float(np.abs(a - e).max()) if rnd else float(np.abs(e - plain.forward64(cfg, w, t)).max())
+             for a, e, t in zip(want, exact, ids)]
+    engine = Engine(load_model(folder, dtype), max_tokens=2 * 1152)
+    slots = [engine.open(), engine.open()]
+    starts = [first, first - 400]  # the second sequence is 400 positions behind: it stays below the bound
+    got = engine.step([(s, t[:n], [n - 1]) for s, t, n in zip(slots, ids, starts)]).cpu().numpy()
+    for i in range(2):
+        assert_logits(got[i:i + 1], want[i][starts[i] - 1:starts[i]], dtype, f"prompt {i}", noise[i])
+    bounds = set()
+    for k in range(last - first + 1):
+        got = engine.step([(s, [t[n + k]], [0]) for s, t, n in zip(slots, ids, starts)]).cpu().numpy()
+        bounds.add(engine.last_batch.position_bound)
+        for i in range(2):
+            assert_logits(got[i:i + 1], want[i][starts[i] + k:starts[i] + k + 1], dtype, f"decode {k} of {i}", noise[i])
+    assert len(bounds) == 2, bounds  # two graphs served the request
+    engine.check_status()
+
+
+@pytest.mark.parametrize("name, dtype", [("B", "float32"), ("D", "bfloat16"), ("A", "bfloat16")])
+def test_steps_that_mix_many_tokens_with_single_ones_and_go_on_by_several(tmp_path, name, dtype):
+    """After their prompts, one sequence brings 30 tokens beside two that bring one; then all three go on by several
+    tokens each (5, 1, 17), twice, so that the second time the step's shape is replayed from a captured graph."""
+    from abacus_b200.engine import Engine, load_model
+    folder = folder_of(tmp_path, name)
+    cfg, w = plain.load(folder)
+    rng = np.random.default_rng(8)
+    prompts, more = [40, 70, 9], [[30, 5, 5], [1, 1, 1], [1, 17, 17]]
+    ids = [random_tokens(rng, p + sum(m), cfg["vocab"]) for p, m in zip(prompts, more)]
+    rnd = plain.bf16_round if dtype == "bfloat16" else None
+    exact = [plain.forward(cfg, w, t) for t in ids]
+    want = [plain.forward(cfg, w, t, rnd=rnd) if rnd else e for t, e in zip(ids, exact)]
+    noise = [float(np.abs(a - e).max()) if rnd else float(np.abs(e - plain.forward64(cfg, w, t)).max())
+             for a, e, t in zip(want, exact, ids)]
+    engine = Engine(load_model(folder, dtype), max_tokens=64 * 8)
+    slots = [engine.open() for _ in ids]
+    at = [0, 0, 0]
+    for counts in [prompts] + [list(c) for c in zip(*more)]:
+        entries = [(s, t[a:a + n], list(range(n))) for s, t, a, n in zip(slots, ids, at, counts)]
+        got = engine.step(entries).cpu().numpy()
+        row = 0
+        for i, n in enumerate(counts):
+            assert_logits(got[row:row + n], want[i][at[i]:at[i] + n], dtype, f"sequence {i} at {at[i]} + {n}", noise[i])
+            row += n
+            at[i] += n
+    engine.check_status()
+    assert engine.prompt_graphs is None or engine.prompt_graphs.replayed >= 1
+
+
+def test_more_single_token_sequences_than_a_captured_step_holds(tmp_path):
+    """300 sequences of one token each in one step, then a second token each: beyond the largest captured decode step
+    (256 rows), so the step runs as it is."""
+    from abacus_b200.engine import Engine, load_model
+    folder = folder_of(tmp_path, "A")
+    cfg, w = plain.load(folder)
+    rng = np.random.default_rng(9)
+    n = 300
+    ids = [random_tokens(rng, 2, cfg["vocab"]) for _ in range(n)]
+    from abacus_b200.engine.graphs import row_bucket
+    assert row_bucket(n) is None
+    exact = np.stack([plain.forward(cfg, w, t) for t in ids])  # [n, 2, vocab]
+    for dtype in ("float32", "bfloat16"):
+        engine = Engine(load_model(folder, dtype), max_tokens=64 * n, max_slots=n)
+        slots = [engine.open() for _ in range(n)]
+        if dtype == "bfloat16":
+            want = np.stack([plain.forward(cfg, w, t, rnd=plain.bf16_round) for t in ids])
+            noise = float(np.abs(want - exact).max())
+        else:
+            want = exact
+            noise = max(float(np.abs(e - plain.forward64(cfg, w, t)).max()) for e, t in zip(exact, ids))
+        for k in range(2):
+            got = engine.step([(s, [t[k]], [0]) for s, t in zip(slots, ids)]).cpu().numpy()
+            assert got.shape == (n, cfg["vocab"])
+            assert_logits(got, want[:, k], dtype, f"{dtype} token {k}", noise=noise)
+        for s in slots:
+            engine.close(s)
+        engine.check_status()

@@ -65,6 +65,34 @@ def test_bpe_merges_lowest_rank_first_and_matches_added_tokens(tmp_path):
     assert tok.decode(tok.encode(text)) == text  # bytes go in, the same bytes come out
 
 
+def test_token_ids_are_abacus_own(tmp_path):
+    """abacus's check begins with identical token ids (tools/check.py:56-61). tests/golden/tokenizer_abacus.json holds
+    what abacus's `--tokenize` (src/main.c:146-149) gives with a synthetic vocabulary of real merges
+    (tests/golden/make_tokenizer_golden.py): plain ASCII, contractions in both cases, digits, runs of blanks, tabs and
+    newlines, code, CJK, accents, Cyrillic and Greek, emoji and symbols, the chat template with its added tokens, an
+    added token cut short. Two more cases are ones where this tokenizer follows Unicode's categories and abacus's C
+    code its coarse classes (src/tokenizer.c:73-88): digits that are not ASCII are digits here (one to a word, as
+    \\p{N} says) and letters there, and a combining accent is no letter here and one there. There the ids differ on
+    purpose, and the words say how."""
+    golden_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    tok = Tokenizer.from_file(os.path.join(golden_dir, "tokenizer_synthetic.json"))
+    with open(os.path.join(golden_dir, "tokenizer_abacus.json")) as f:
+        golden = json.load(f)
+    assert golden["merges"] >= 150 and len(golden["cases"]) >= 19
+    kinds = set()
+    for case in golden["cases"]:
+        kinds.add(case["kind"])
+        ids = tok.encode(case["text"])
+        assert tok.decode(ids, skip_special=False) == case["text"]
+        if case["kind"] == "unicode":
+            assert ids != case["ids"], case["text"]
+        else:
+            assert ids == case["ids"], case["text"]
+    assert kinds == {"ascii", "beyond", "added", "unicode"}
+    assert words("\u0663\u0664 apples") == ["\u0663", "\u0664", " apples"]  # \p{N}: one digit a word
+    assert words("e\u0301te") == ["e", "\u0301te"]  # the accent is no letter: it ends a word and leads the next
+
+
 def test_options_keep_abacus_names_and_defaults():
     o = parse(["model"])
     assert (o.steps, o.temp, o.raw, o.prompt, o.top_k) == (512, 0.7, False, "Why is the ocean salty?", 20)  # src/main.c:109-112
