@@ -15,6 +15,7 @@ from dataclasses import dataclass
 
 import torch
 
+from ..kernels import guards
 from .need import CacheNeed
 from .pages import CacheFull, FreeList, PageBook
 
@@ -52,8 +53,8 @@ class _Group:
         self.table_width = max(1, min(per_seq, n_pages))
         self.book = PageBook(n_pages, tpp, self.ring_pages)
         shape = (len(entries), n_pages, need.n_kv_heads, tpp, need.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.k = guards.zeros(shape, dtype, device, what="cache keys")  # guard words around the pools
+        self.v = guards.zeros(shape, dtype, device, what="cache values")
         # pageable on purpose: a copy from pageable memory is staged before copy_ returns, so the
         # host may rewrite a row (a slot used again) while earlier steps are still in flight
         self.table_host = torch.zeros((max_slots, self.table_width), dtype=torch.int32)
@@ -80,7 +81,8 @@ class SequenceCache:
                 key = (need.n_kv_heads, need.head_dim, need.window)
                 by_need.setdefault(key, []).append(e)
             if need.state_shape:
-                self.states[e] = torch.zeros((self.max_slots, *need.state_shape), dtype=torch.float32, device=device)
+                self.states[e] = guards.zeros((self.max_slots, *need.state_shape), torch.float32, device,
+                                              what=f"state of entry {e}")
         for (hkv, hd, window), entries in by_need.items():
             g = _Group(CacheNeed(hkv, hd, window), entries, self.n_pages, self.max_slots, self.max_context, dtype,
                        self.device)

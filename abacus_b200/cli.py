@@ -23,7 +23,7 @@ USAGE = """usage: abacus MODEL [options]
                    feeding the ids in chunks of --chunk C (default: all at once)
   --info           print the model shape and weight format
   --fp32           run everything in true 32-bit floating point (default: bfloat16)
-  --top-k K        sample among the K most likely tokens (default 20, at most 64)
+  --top-k K        sample among the K most likely tokens (default 20, at most 64; 0: all tokens)
   --batch B        with --bench: B sequences at once (default 1)
   -t N, --q4       abacus's CPU threads and 4-bit weights: not built here
 """

@@ -110,6 +110,16 @@ template <int EPL> __global__ void __launch_bounds__(DEC_THREADS) attn_decode_ke
         return;
     }
     const int pos = p.token_pos[r];
+    if (pos >= p.max_chunks * DEC_CHUNK) {
+        // The row lies beyond the bound the grid was sized for: not all of its chunks have a CTA, so nobody would
+        // draw the last ticket. Say so in the status word, leave zeros, and touch no ticket.
+        if (chunk == 0) {
+            if (threadIdx.x == 0) atomicOr(p.status + 2, 2);
+            for (int i = threadIdx.x; i < group * HD; i += DEC_THREADS)
+                p.out[((long long)r * p.n_heads + kvh * group) * HD + i] = __float2bfloat16_rn(0.0f);
+        }
+        return;
+    }
     const int lo = p.window > 0 && pos - p.window + 1 > 0 ? pos - p.window + 1 : 0;
     const int first = chunk * DEC_CHUNK;
     if (first > pos || first + DEC_CHUNK <= lo) return;  // none of this chunk's keys is visible

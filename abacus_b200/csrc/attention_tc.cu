@@ -411,7 +411,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attn_prefill_tc_kernel(const __
             if (threadIdx.x == 0) {
                 const uint64_t t0 = tc::global_ns();
                 int seen = 0;
-                while (!(seen = atomicAdd(p.tickets + 2 * pair + 1, 0)) && tc::global_ns() - t0 < TC_WAIT_NS) __nanosleep(100);
+                while (!(seen = atomicAdd(p.tickets + 2 * pair + 1, 0)) && tc::global_ns() - t0 < tc::abk_wait_limit_ns) __nanosleep(100);
                 if (!seen) atomicOr(p.status + 3, 512), *failed = 1;
                 p.tickets[2 * pair] = 0, p.tickets[2 * pair + 1] = 0;  // as they were, for the next launch
                 *(volatile int *)swap = seen;

@@ -262,3 +262,106 @@ extern "C" int abk_sample_topk(const float *logits, long long row_stride, int n_
                temp, top_k, rng, rng_index, out, (Best *)scratch, tickets);
     return ABK_LAUNCH_RESULT();
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// A draw from the whole vocabulary at a temperature (top_k = 0). abacus always cuts to the 20 most likely tokens
+// (src/main.c:41); without the cut there is no short list to sort, so the tokens are walked in index order instead of
+// by falling logit. The distribution is the same, p_j = exp((l_j - l_max) / temperature) over all j, and so is the
+// generator (xorshift64, src/main.c:52): r = u24 / 2^24 * sum, the token is the first j whose running sum reaches r.
+// Sums are float64 over float32 terms, so the grouping of the additions cannot move a boundary.
+//   sample_all_sums_kernel: a block adds up p_j over its ALL_BLOCK logits.
+//   sample_all_draw_kernel: one block a row: running sums of the blocks in order, the block r falls into, the walk in it.
+#define ALL_BLOCK 1024
+#define ALL_THREADS 256
+#define ALL_MAX_BLOCKS 1024
+
+__global__ void __launch_bounds__(ALL_THREADS) sample_all_sums_kernel(const float *__restrict__ logits, long long row_stride,
+                                                                      int vocab, float inv_temp, const int *__restrict__ top,
+                                                                      double *__restrict__ sums) {
+    __shared__ double warp_sum_s[ALL_THREADS / 32];
+    pdl_wait();
+    const int row = blockIdx.y, lo = blockIdx.x * ALL_BLOCK, hi = min(vocab, lo + ALL_BLOCK);
+    const float *x = logits + (long long)row * row_stride;
+    const float m = x[top[row]];
+    double acc = 0.0;
+    for (int j = lo + threadIdx.x; j < hi; j += ALL_THREADS) acc += (double)expf((x[j] - m) * inv_temp);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) warp_sum_s[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < ALL_THREADS / 32; w++) t += warp_sum_s[w];
+        sums[(long long)row * gridDim.x + blockIdx.x] = t;
+    }
+}
+
+__global__ void __launch_bounds__(ALL_THREADS) sample_all_draw_kernel(const float *__restrict__ logits, long long row_stride,
+                                                                      int vocab, float inv_temp, const int *__restrict__ top,
+                                                                      const double *__restrict__ sums, int n_blocks,
+                                                                      unsigned long long *rng, const int *rng_index,
+                                                                      int *__restrict__ out) {
+    __shared__ double before_block[ALL_MAX_BLOCKS + 1];  // running sum of the blocks before block b
+    __shared__ float p_s[ALL_BLOCK];
+    __shared__ int block_of_r;
+    __shared__ double r_s;
+    pdl_wait();
+    const int row = blockIdx.x;
+    const float *x = logits + (long long)row * row_stride;
+    const float m = x[top[row]];
+    if (threadIdx.x == 0) {
+        double run = 0.0;
+        for (int b = 0; b < n_blocks; b++) {
+            before_block[b] = run;
+            run += sums[(long long)row * n_blocks + b];
+        }
+        before_block[n_blocks] = run;
+        const int which = rng_index ? rng_index[row] : row;
+        unsigned long long s = rng[which];
+        s ^= s << 13, s ^= s >> 7, s ^= s << 17;
+        rng[which] = s;
+        const double r = (double)(s >> 40) / (double)(1 << 24) * run;
+        int b = 0;
+        while (b + 1 < n_blocks && before_block[b + 1] < r) b++;  // the first block whose running sum reaches r
+        block_of_r = b, r_s = r;
+    }
+    __syncthreads();
+    const int lo = block_of_r * ALL_BLOCK, hi = min(vocab, lo + ALL_BLOCK);
+    for (int j = lo + threadIdx.x; j < hi; j += ALL_THREADS) p_s[j - lo] = expf((x[j] - m) * inv_temp);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double run = before_block[block_of_r];
+        int chosen = hi - 1;  // (rounding left r a hair above the block's last running sum)
+        for (int j = lo; j < hi; j++) {
+            run += (double)p_s[j - lo];
+            if (run >= r_s) {
+                chosen = j;
+                break;
+            }
+        }
+        out[row] = chosen;
+    }
+}
+
+// Bytes of scratch abk_sample_all needs for n_rows rows of a vocabulary.
+extern "C" long long abk_sample_all_scratch_bytes(int n_rows, int vocab) {
+    return (long long)n_rows * ((vocab + ALL_BLOCK - 1) / ALL_BLOCK) * (long long)sizeof(double);
+}
+// top: int32 [n_rows], the index of each row's maximum (abk_argmax gives it); scratch as above.
+extern "C" int abk_sample_all(const float *logits, long long row_stride, int n_rows, int vocab, float temp, const int *top,
+                              unsigned long long *rng, const int *rng_index, int *out, void *scratch, void *stream) {
+    if (n_rows <= 0) return 0;
+    if (vocab < 1) ABK_REFUSE("sample: vocabulary of %d", vocab);
+    if (!(temp > 0.0f)) ABK_REFUSE("sample: temperature %g is not positive (use argmax)", temp);
+    const int n_blocks = (vocab + ALL_BLOCK - 1) / ALL_BLOCK;
+    if (n_blocks > ALL_MAX_BLOCKS) ABK_REFUSE("sample: a vocabulary of %d is more than %d blocks of %d", vocab, ALL_MAX_BLOCKS, ALL_BLOCK);
+    if (n_rows > 65535) ABK_REFUSE("sample: %d rows exceed a grid", n_rows);
+    abk_launch(sample_all_sums_kernel, dim3(n_blocks, n_rows), dim3(ALL_THREADS), 0, (cudaStream_t)stream, logits, row_stride,
+               vocab, 1.0f / temp, top, (double *)scratch);
+    int rc = ABK_LAUNCH_RESULT();
+    if (rc) return rc;
+    abk_launch(sample_all_draw_kernel, dim3(n_rows), dim3(ALL_THREADS), 0, (cudaStream_t)stream, logits, row_stride, vocab,
+               1.0f / temp, top, (const double *)scratch, n_blocks, rng, rng_index, out);
+    return ABK_LAUNCH_RESULT();
+}
+

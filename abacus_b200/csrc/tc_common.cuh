@@ -36,10 +36,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// Waits for the phase with the given parity; false if it did not come within TC_WAIT_NS of wall
-// time (a quarter of a second: thousands of times longer than any wait of a working kernel, and
-// short enough that a kernel whose barriers are wrong ends at once instead of spinning for minutes).
+// Waits for the phase with the given parity; false if it did not come within the library's limit of wall time. The
+// limit starts at a quarter of a second: thousands of times longer than any wait of a working kernel, and short
+// enough that a kernel whose barriers are wrong ends at once instead of spinning for minutes. It is a variable of
+// the library on the device, so a caller (a test that lets a wait run out on purpose) can set it at run time.
 #define TC_WAIT_NS 250000000ull
+__device__ unsigned long long abk_wait_limit_ns = TC_WAIT_NS;
+#ifdef ABK_DEFINE_ERROR
+// Sets the limit of every bounded wait of this library's kernels on the current device, in nanoseconds.
+extern "C" int abk_set_wait_limit_ns(unsigned long long ns) {
+    return (int)cudaMemcpyToSymbol(abk_wait_limit_ns, &ns, sizeof ns);
+}
+#endif
 __device__ __forceinline__ uint64_t global_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -47,11 +55,11 @@ __device__ __forceinline__ uint64_t global_ns() {
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t start = global_ns();
+    const uint64_t start = global_ns(), limit = abk_wait_limit_ns;
     for (;;) {
         for (int i = 0; i < 64; i++)
             if (mbar_try_wait(bar, parity)) return true;
-        if (global_ns() - start > TC_WAIT_NS) return false;
+        if (global_ns() - start > limit) return false;
     }
 }
 

@@ -13,8 +13,14 @@
 // Guard words. A buffer handed out with guards has ABK_GUARD_WORDS words of a fixed pattern before and
 // after it; abk_guard_check counts the words that no longer hold the pattern. With no memory checker on
 // the device, this is what shows a store past the end of a workspace, a scratch area or a cache pool.
+//
+// A wait that runs out. Every wait of the kernels on a barrier is bounded (tc_common.cuh) and ends in a status word
+// instead of a hang. abk_wait_that_runs_out is the smallest kernel with such a wait: a barrier that expects bytes
+// nobody sends. It exists so that the way from a wait that ran out to the host's exception can be walked without
+// breaking anything: the kernel returns, the context stays usable.
 #define ABK_DEFINE_ERROR
 #include "common.cuh"
+#include "tc_common.cuh"
 
 __host__ __device__ __forceinline__ unsigned long long abk_mix64(unsigned long long x) {
     x ^= x >> 30;
@@ -86,3 +92,21 @@ extern "C" int abk_guard_check(const void *words, int n, int *damaged, void *str
     guard_check_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const unsigned int *)words, n, damaged);
     return ABK_LAUNCH_RESULT();
 }
+
+__global__ void wait_that_runs_out_kernel(int *status, int bit) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        tc::mbar_init(&bar, 1);
+        tc::mbar_init_fence();
+        tc::mbar_expect_tx(&bar, 16);             // 16 bytes that no copy will ever bring
+        if (!tc::mbar_wait(&bar, 0)) atomicOr(status, bit);
+    }
+}
+
+// Runs a kernel whose only wait cannot be satisfied and therefore runs out after this library's limit
+// (abk_set_wait_limit_ns); it then sets `bit` in *status and returns.
+extern "C" int abk_wait_that_runs_out(int *status, int bit, void *stream) {
+    wait_that_runs_out_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, bit);
+    return ABK_LAUNCH_RESULT();
+}
+

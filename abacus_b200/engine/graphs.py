@@ -85,6 +85,9 @@ class DecodeGraph:
     def replay_advanced(self):
         """Replay after moving every row one position on, on the device; the tokens are whatever the
         token buffer holds (a sampler may have written them there). Nothing comes from the host."""
+        if self.position_bound is not None and self.batch.max_len_after + 1 > self.position_bound:
+            raise ValueError(f"a row would move to position {self.batch.max_len_after}, beyond the bound "
+                             f"{self.position_bound} this graph was captured for")
         self.batch.advance_on_device()
         self.graph.replay()
         return self.logits[:self.batch.n_seqs]

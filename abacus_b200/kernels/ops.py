@@ -9,6 +9,7 @@ import ctypes
 
 import torch
 
+from . import guards
 from .build import load_module
 
 F32, BF16 = 0, 1
@@ -275,6 +276,25 @@ def sample_topk(logits, temperature, top_k, rng_state, out, n_rows=None, rng_ind
                                     _p(sc.sample_tickets), _stream()), "sample_topk")
 
 
+def sample_all(logits, temperature, rng_state, out, n_rows=None, rng_index=None):
+    """Draw from the whole vocabulary at a temperature (top_k = 0): p_j = exp((l_j - l_max) / temperature) over all j,
+    walked in index order with abacus's generator (src/main.c:49-55 without the cut to 20 of src/main.c:41)."""
+    _need_cuda(logits, rng_state, out, rng_index)
+    lib = load_module("sampling")
+    lib.abk_sample_all_scratch_bytes.restype = ctypes.c_longlong
+    n = logits.shape[0] if n_rows is None else n_rows
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32 and out.numel() >= n
+    assert rng_state.dtype == torch.int64
+    assert rng_index is None or (rng_index.dtype == torch.int32 and rng_index.numel() >= n)
+    assert rng_index is not None or rng_state.numel() >= n
+    sc = _Scratch.of(logits.device)
+    top = sc.grown("sample_all_top", n, torch.int32)
+    sums = sc.grown("sample_all_sums", lib.abk_sample_all_scratch_bytes(_i(n), _i(logits.shape[1])), torch.uint8)
+    argmax(logits, top, n)
+    _check(lib, lib.abk_sample_all(_p(logits), _ll(logits.stride(0)), _i(n), _i(logits.shape[1]), _f(temperature), _p(top),
+                                   _p(rng_state), _p(rng_index), _p(out), _p(sums), _stream()), "sample_all", kernels=2)
+
+
 def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, ws=None):
     """Attention of a step: picks the kernel for the phase and sizes; every case the faster kernels
     do not take goes to the general one."""
@@ -394,6 +414,13 @@ class _Scratch:
         self.argmax_rows = 4096
         self._made = {}
 
+    def grown(self, name, count, dtype):
+        """A buffer of at least `count` elements that is kept and only ever replaced by a larger one."""
+        have = self._made.get(name)
+        if have is None or have.numel() < count or have.dtype != dtype:
+            have = self._made[name] = guards.empty(max(int(count), 1), dtype, self.device, what=f"scratch {name}")
+        return have
+
     def _lazy(self, name, make):
         # each kernel's scratch is made at that kernel's first use, so that a model loads
         # (and compiles) only the kernel libraries it runs
@@ -406,18 +433,18 @@ class _Scratch:
         def make():
             lib = load_module("gemm_tc")
             lib.abk_gemm_tc_scratch_floats.restype = ctypes.c_longlong
-            return torch.empty(lib.abk_gemm_tc_scratch_floats(), dtype=torch.float32, device=self.device)
+            return guards.empty(lib.abk_gemm_tc_scratch_floats(), torch.float32, self.device, what="scratch of split K")
         return self._lazy("gemm_floats", make)
 
     @property
     def gemm_tickets(self):
-        return self._lazy("gemm_tickets", lambda: torch.zeros(load_module("gemm_tc").abk_gemm_tc_scratch_tickets(),
-                                                              dtype=torch.int32, device=self.device))
+        return self._lazy("gemm_tickets", lambda: guards.zeros(load_module("gemm_tc").abk_gemm_tc_scratch_tickets(),
+                                                               torch.int32, self.device, what="tickets of split K"))
 
     @property
     def argmax_part(self):
-        return self._lazy("argmax_part", lambda: torch.empty(
-            self.argmax_rows * load_module("sampling").abk_argmax_slices() * 2, dtype=torch.float32, device=self.device))
+        return self._lazy("argmax_part", lambda: guards.empty(
+            self.argmax_rows * load_module("sampling").abk_argmax_slices() * 2, torch.float32, self.device, what="scratch of argmax"))
 
     sample_rows = 1024
 
@@ -426,16 +453,17 @@ class _Scratch:
         def make():
             lib = load_module("sampling")
             lib.abk_sample_topk_scratch_bytes.restype = ctypes.c_longlong
-            return torch.empty(lib.abk_sample_topk_scratch_bytes(_i(self.sample_rows)), dtype=torch.uint8, device=self.device)
+            return guards.empty(lib.abk_sample_topk_scratch_bytes(_i(self.sample_rows)), torch.uint8, self.device,
+                                what="scratch of sampling")
         return self._lazy("sample_part", make)
 
     @property
     def sample_tickets(self):
-        return self._lazy("sample_tickets", lambda: torch.zeros(self.sample_rows, dtype=torch.int32, device=self.device))
+        return self._lazy("sample_tickets", lambda: guards.zeros(self.sample_rows, torch.int32, self.device, what="tickets of sampling"))
 
     @property
     def argmax_tickets(self):
-        return self._lazy("argmax_tickets", lambda: torch.zeros(self.argmax_rows, dtype=torch.int32, device=self.device))
+        return self._lazy("argmax_tickets", lambda: guards.zeros(self.argmax_rows, torch.int32, self.device, what="tickets of argmax"))
 
     attention_halves_pairs = 384  # (tile, head) pairs the prefill attention may halve in one launch (engine/batch.py)
 
@@ -445,17 +473,18 @@ class _Scratch:
             lib = load_module("attention_tc")
             lib.abk_attention_prefill_tc_scratch_floats.restype = ctypes.c_longlong
             floats = lib.abk_attention_prefill_tc_scratch_floats(_i(self.attention_halves_pairs), _i(1))
-            return torch.empty(floats, dtype=torch.float32, device=self.device)
+            return guards.empty(floats, torch.float32, self.device, what="scratch of halved attention tiles")
         return self._lazy("attention_halves", make)
 
     @property
     def attention_halves_tickets(self):
         return self._lazy("attention_halves_tickets",
-                          lambda: torch.zeros(2 * self.attention_halves_pairs, dtype=torch.int32, device=self.device))
+                          lambda: guards.zeros(2 * self.attention_halves_pairs, torch.int32, self.device,
+                                               what="tickets of halved attention tiles"))
 
     @property
     def attention_tickets(self):
-        return self._lazy("attention_tickets", lambda: torch.zeros(1 << 18, dtype=torch.int32, device=self.device))
+        return self._lazy("attention_tickets", lambda: guards.zeros(1 << 18, torch.int32, self.device, what="tickets of decode attention"))
 
     @classmethod
     def of(cls, device):
@@ -470,6 +499,27 @@ def _attention_tickets(device, n):
     if n > sc.attention_tickets.numel():
         raise KernelRefused(f"attention_decode: {n} (row, kv head) pairs are more than its {sc.attention_tickets.numel()} tickets")
     return sc.attention_tickets
+
+
+def set_wait_limit_ns(ns, modules=("utility",)):
+    """The limit of the bounded waits (on barriers, on another CTA's flag) of the named kernel libraries on the current
+    device: a wait that has not been satisfied after `ns` nanoseconds gives up, the kernel sets its status word and
+    returns. The libraries start at a quarter of a second."""
+    for module in modules:
+        lib = load_module(module)
+        rc = lib.abk_set_wait_limit_ns(ctypes.c_ulonglong(int(ns)))
+        if rc:
+            raise KernelError(f"set_wait_limit_ns({module}): CUDA error {rc}")
+
+
+def wait_that_runs_out(status, bit=4, word=1):
+    """Launches the kernel whose one wait nothing can satisfy (csrc/utility.cu): after the utility library's limit it
+    sets `bit` in status[word] and returns. For walking the way from a wait that ran out to the host's exception."""
+    _need_cuda(status)
+    lib = load_module("utility")
+    assert status.dtype == torch.int32 and status.numel() > word
+    _check(lib, lib.abk_wait_that_runs_out(ctypes.c_void_p(status.data_ptr() + 4 * word), _i(bit), _stream()),
+           "wait_that_runs_out")
 
 
 def kernel_status(device):

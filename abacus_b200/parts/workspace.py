@@ -1,10 +1,13 @@
 """Scratch tensors of a step, kept between steps and shared by all layers.
 
-`get(name, shape, dtype)` returns a view of a buffer that only ever grows.
+`get(name, shape, dtype)` returns a view of a buffer that only ever grows (with guard words around it,
+kernels/guards.py).
 `generation` goes up whenever a buffer is replaced, so that whoever holds
 addresses (a captured CUDA graph) knows they are stale.
 """
 import torch
+
+from ..kernels import guards
 
 
 class Workspace:
@@ -24,7 +27,7 @@ class Workspace:
         key = (name, dtype)
         buf = self._buffers.get(key)
         if buf is None or buf.numel() < count:
-            buf = torch.empty(max(count, 1), dtype=dtype, device=self.device)
+            buf = guards.empty(max(count, 1), dtype, self.device, what=f"workspace {name}")
             self._buffers[key] = buf
             self.generation += 1
             self._views = {k: v for k, v in self._views.items() if (k[0], k[2]) != key}

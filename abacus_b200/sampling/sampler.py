@@ -27,12 +27,13 @@ def as_signed(u):
 
 class Sampler:
     """temperature <= 0: first maximum (src/main.c:31-36). Else: draw among the top_k logits with
-    p_j = exp((l_j - l_max) / temperature) (src/main.c:39-56; abacus fixes top_k at 20)."""
+    p_j = exp((l_j - l_max) / temperature) (src/main.c:39-56; abacus fixes top_k at 20). top_k = 0: the whole
+    vocabulary, walked in index order instead of by falling logit (the same distribution, no list to sort)."""
 
     def __init__(self, device, temperature=0.7, top_k=20, seed=0):
         self.device, self.temperature, self.top_k, self.seed = device, float(temperature), int(top_k), int(seed)
-        if self.temperature > 0 and not 1 <= self.top_k <= 64:
-            raise ValueError(f"top_k {top_k} is not in 1..64")
+        if self.temperature > 0 and not 0 <= self.top_k <= 64:
+            raise ValueError(f"top_k {top_k} is neither 0 (the whole vocabulary) nor in 1..64")
 
     @property
     def greedy(self):
@@ -51,6 +52,8 @@ class Sampler:
             out = torch.empty(n, dtype=torch.int32, device=logits.device)
         if self.greedy:
             ops.argmax(logits, out, n)
+        elif self.top_k == 0:
+            ops.sample_all(logits, self.temperature, states, out, n, rng_index=index)
         else:
             ops.sample_topk(logits, self.temperature, self.top_k, states, out, n, rng_index=index)
         return out

@@ -21,3 +21,16 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def guard_words_are_intact():
+    """After every test that ran on the GPU: no kernel stored outside a workspace, a scratch area or a cache pool
+    (abacus_b200/kernels/guards.py)."""
+    yield
+    guards = sys.modules.get("abacus_b200.kernels.guards")
+    if guards is not None and guards._buffers:
+        import torch
+        if torch.cuda.is_available():
+            guards.assert_intact()
+

@@ -251,9 +251,21 @@ def xorshift64(state):
 
 
 def sample(logits, temp, state, top_k=20):
-    """Top-20 sampling at a temperature; returns (token, new state) (src/main.c:39-56)."""
+    """Top-20 sampling at a temperature; returns (token, new state) (src/main.c:39-56).
+
+    top_k = 0 is this library's own: no cut to the most likely tokens (src/main.c:41), the same probabilities
+    exp((l_j - l_max) / temp) over the whole vocabulary, the same generator, and the walk of src/main.c:53-55 in
+    index order, since there is no sorted short list; sums in float64."""
     if temp <= 0.0:
         return argmax(logits), state
+    if top_k == 0:
+        x = np.asarray(logits, dtype=F32)
+        p = np.exp((x - x[argmax(x)]) * F32(F32(1.0) / F32(temp)), dtype=F32).astype(np.float64)
+        run = np.cumsum(p)
+        state = xorshift64(state)
+        r = float(state >> 40) / float(1 << 24) * run[-1]
+        hit = np.flatnonzero(run >= r)
+        return (int(hit[0]) if len(hit) else len(x) - 1), state
     top = []
     for i in range(len(logits)):
         if len(top) == top_k and logits[i] <= logits[top[-1]]:

@@ -48,6 +48,24 @@ def test_random_fill_is_the_same_bits_on_the_device_and_on_the_host(ops):
     assert ri.tensor_key(3, "a") != ri.tensor_key(4, "a") != ri.tensor_key(4, "b")
 
 
+def test_guard_words_show_a_store_outside_a_buffer(ops):
+    """A buffer made by kernels/guards.py has 256 bytes of a pattern on either side. Overwriting one of them (here with
+    a plain copy into the allocation's own guard: nothing outside it is touched) is found by the check, and named."""
+    from abacus_b200.kernels import guards
+    t = guards.zeros((3, 50), torch.float32, "cuda", what="a test buffer")
+    assert t.shape == (3, 50) and float(t.abs().sum()) == 0.0 and guards.check()[0] == 0
+    whole = t.guarded_allocation
+    after = guards.GUARD_BYTES + 768  # 600 bytes of data, rounded up to 768: the guard behind starts here
+    saved = whole[after:after + 8].clone()
+    whole[after + 4:after + 8] = 0  # what a kernel that stored one float too far would have done
+    damaged, where = guards.check()
+    assert damaged == 1 and where == ["a test buffer"]
+    with pytest.raises(RuntimeError, match="a test buffer"):
+        guards.assert_intact()
+    whole[after:after + 8] = saved
+    assert guards.check()[0] == 0
+
+
 def test_embed(ops):
     rng = np.random.default_rng(0)
     table = bf(rng.standard_normal((1000, 72)))
@@ -162,6 +180,51 @@ def test_sample_topk_draws_what_the_plain_sampler_draws(ops, temp, top_k):
         ops.sample_topk(ld, 0.0, 5, st, out)
 
 
+@pytest.mark.parametrize("vocab, temp", [(2311, 0.8), (70001, 1.3), (151936, 0.6), (1024, 2.0), (5, 1.0)])
+def test_sampling_from_the_whole_vocabulary(ops, vocab, temp):
+    """top_k = 0: every token can be drawn. The same tokens as the plain sampler, row by row and draw by draw; rows with
+    ties, with all logits equal, with -inf entries; and over many draws from a short row, every token with its share."""
+    rng = np.random.default_rng(vocab)
+    rows = 12
+    logits = (2 * rng.standard_normal((rows, vocab))).astype(np.float32)
+    logits[1, :] = 0.25                                   # all equal: uniform over the vocabulary
+    logits[2, vocab // 2:] = np.float32(-np.inf)          # half of the tokens impossible
+    logits[3, [0, vocab - 1]] = logits[3].max() + 3.0     # a tie at the top, first and last token
+    states = [int(s) for s in rng.integers(1, 2 ** 62, rows)]
+    st, want_states = dev(states, torch.int64), list(states)
+    index = dev(list(range(rows))[::-1], torch.int32)
+    ld, out = dev(logits), torch.empty(rows, dtype=torch.int32, device="cuda")
+    for step in range(6):
+        ops.sample_all(ld, temp, st, out, rng_index=index)
+        got = out.tolist()
+        for r in range(rows):
+            tok, want_states[rows - 1 - r] = plain.sample(logits[r], temp, want_states[rows - 1 - r], top_k=0)
+            assert got[r] == tok, (step, r)
+        assert got[2] < vocab // 2 or vocab < 4
+    assert [v % (1 << 64) for v in st.tolist()] == want_states
+    if vocab == 5:  # the shares: 4,000 draws from five tokens
+        flat = dev(np.tile(np.array([[0.0, 1.0, -1.0, 0.5, 0.0]], dtype=np.float32), (1000, 1)))
+        st = dev([int(s) for s in rng.integers(1, 2 ** 62, 1000)], torch.int64)
+        out, counts = torch.empty(1000, dtype=torch.int32, device="cuda"), np.zeros(5)
+        for _ in range(4):
+            ops.sample_all(flat, 1.0, st, out)
+            counts += np.bincount(out.cpu().numpy(), minlength=5)
+        p = np.exp([0.0, 1.0, -1.0, 0.5, 0.0])
+        assert np.abs(counts / 4000 - p / p.sum()).max() < 0.03
+
+
+def test_a_zero_seed_draws_like_any_other():
+    """xorshift64 cannot leave state 0, so the sampler never starts a request there: with seed 0 and a temperature the
+    first request's draws from a flat row are not all the first token (which a dead stream would give)."""
+    from abacus_b200.sampling import Sampler
+    sampler = Sampler(torch.device("cuda", 0), temperature=1.0, top_k=20, seed=0)
+    states = sampler.states([0, 1])
+    assert 0 not in states.tolist()
+    flat = torch.zeros(2, 500, device="cuda")
+    drawn = [sampler.sample(flat, states).tolist() for _ in range(12)]
+    assert len({d[0] for d in drawn}) > 3 and len({d[1] for d in drawn}) > 3
+
+
 @pytest.mark.parametrize("top_k", [20, 64])
 def test_sample_topk_on_a_large_vocabulary(ops, top_k):
     """Slices of more than a thousand logits take the two-pass way (a bound from the threads' maxima, then the
@@ -200,9 +263,10 @@ class Harness:
         self.cache = SequenceCache([CacheNeed(hkv, hd, window)], [None], max_tokens, dtype, "cuda", max_context=1024)
 
     def step(self, ops, seqs, qkv, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved, scale, from_step=False,
-             general=True):
+             general=True, simt=False):
         """seqs: [(slot, n_new)]; qkv float32 numpy [rows, (hq + 2 hkv) * hd]. Returns attention output.
-        general=False lets ops.attention pick the kernel for the phase, as the model does."""
+        general=False lets ops.attention pick the kernel for the phase, as the model does; simt=True sends a decode
+        step to the CUDA-core decode kernel whatever the head size."""
         from abacus_b200.engine.batch import Sequence, StepBatch
         ss = []
         for slot, n in seqs:
@@ -217,6 +281,10 @@ class Harness:
         out = torch.full((rows + 3, self.hq * self.hd), 5.0, dtype=self.dtype, device="cuda")
         if general:
             ops.attention_generic(q, out, self.hq, self.hkv, self.hd, scale, self.window, batch, kv, from_step=from_step)
+        elif simt:
+            from abacus_b200.parts import Workspace
+            self.ws = getattr(self, "ws", None) or Workspace(torch.device("cuda", 0))
+            ops.attention_decode(q, out, self.hq, self.hkv, self.hd, scale, self.window, batch, kv, self.ws, simt=True)
         else:
             from abacus_b200.parts import Workspace
             self.ws = getattr(self, "ws", None) or Workspace(torch.device("cuda", 0))
@@ -283,8 +351,8 @@ def test_qkv_prep_and_attention(ops, dtype, hq, hkv, hd, rotary_dim, interleaved
         q, k, v = plain_prep(qkv, hq, hkv, hd, qn, kn, eps, cos, sin, rotary_dim, interleaved, 0)
         if dtype == torch.bfloat16:
             q, k = bf(q), bf(k)
-        want[key] = (q, plain.attention((q * np.float32(scale * np.sqrt(hd))).astype(np.float32), k, v,
-                                        window).reshape(lens[key], hq * hd))
+        want[key] = (q, plain.attention((q * np.float32(scale * np.sqrt(hd))).astype(np.float32), k, v, window,
+                                        rnd=bf if dtype == torch.bfloat16 else None).reshape(lens[key], hq * hd))
     h = Harness(hq, hkv, hd, dtype, window)
     sa, sb = h.cache.open_slot(), h.cache.open_slot()
     args = (dev(qn) if norm else None, dev(kn) if norm else None, eps, dev(cos), dev(sin), rotary_dim, interleaved,
@@ -454,11 +522,15 @@ def test_gemm_tc_refuses_what_tma_cannot_address(ops):
         ops.gemm_tc(x, w, out)
 
 
-@pytest.mark.parametrize("hq, hkv, hd, window", [(16, 8, 128, None), (6, 2, 64, None), (4, 4, 256, None),
-                                                 (8, 1, 64, None), (4, 2, 128, 200), (3, 1, 128, 64), (10, 2, 64, 129)])
-def test_decode_attention_split_along_the_keys(ops, hq, hkv, hd, window):
+@pytest.mark.parametrize("hq, hkv, hd, window, simt", [
+    (16, 8, 128, None, False), (6, 2, 64, None, False), (4, 4, 256, None, False), (8, 1, 64, None, False),
+    (4, 2, 128, 200, False), (3, 1, 128, 64, False), (10, 2, 64, 129, False),
+    # the CUDA-core kernel at the head sizes the tensor-core one usually takes, with and without windows
+    (16, 8, 128, None, True), (6, 2, 64, 64, True), (4, 2, 128, 129, True), (3, 1, 64, 200, True), (4, 4, 256, 200, True)])
+def test_decode_attention_split_along_the_keys(ops, hq, hkv, hd, window, simt):
     """Rows of very different lengths (1 key to 700: up to six chunks of 128, chunk and page edges
-    included) decoded in one step by the kernel the model uses for decode, against plain attention."""
+    included) decoded in one step by the kernel the model uses for decode (or, with simt, by the
+    CUDA-core decode kernel), against plain attention."""
     rng = np.random.default_rng(hq * 100 + hd + (window or 0))
     lens = [1, 64, 65, 128, 129, 257, 700, 383]
     width = (hq + 2 * hkv) * hd
@@ -473,13 +545,14 @@ def test_decode_attention_split_along_the_keys(ops, hq, hkv, hd, window):
         if len(d) > 1:
             h.step(ops, [(slot, len(d) - 1)], d[:-1], *none, from_step=window is not None)
     # the decode step: one row per sequence, plus the harness's padding rows
-    _, got = h.step(ops, [(slot, 1) for slot in slots], np.concatenate([d[-1:] for d in data]), *none, general=False)
+    _, got = h.step(ops, [(slot, 1) for slot in slots], np.concatenate([d[-1:] for d in data]), *none, general=False,
+                    simt=simt)
     for i, d in enumerate(data):
         n = len(d)
         q = d[:, :hq * hd].reshape(n, hq, hd)
         k = d[:, hq * hd:(hq + hkv) * hd].reshape(n, hkv, hd)
         v = d[:, (hq + hkv) * hd:].reshape(n, hkv, hd)
-        want = plain.attention(q, k, v, window)[-1].reshape(hq * hd)
+        want = plain.attention(q, k, v, window, rnd=bf)[-1].reshape(hq * hd)
         np.testing.assert_allclose(got[i], want, rtol=2 ** -7, atol=2 ** -7, err_msg=f"row {i} of length {n}")
     assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
 
@@ -508,7 +581,7 @@ def test_prefill_attention_on_the_tensor_cores(ops, hq, hkv, hd):
         q = d[:, :hq * hd].reshape(n, hq, hd)
         k = d[:, hq * hd:(hq + hkv) * hd].reshape(n, hkv, hd)
         v = d[:, (hq + hkv) * hd:].reshape(n, hkv, hd)
-        want = plain.attention(q, k, v).reshape(n, hq * hd)
+        want = plain.attention(q, k, v, rnd=bf).reshape(n, hq * hd)
         m = len(first[i])
         got = got1[at:at + m] if i != 4 else np.concatenate([got1[at:at + m], got2])
         at += m
@@ -544,7 +617,7 @@ def test_prefill_attention_halves_long_tiles(ops):
                 q = d[:, :hq * hd].reshape(n, hq, hd)
                 k = d[:, hq * hd:(hq + hkv) * hd].reshape(n, hkv, hd)
                 v = d[:, (hq + hkv) * hd:].reshape(n, hkv, hd)
-                np.testing.assert_allclose(g, plain.attention(q, k, v).reshape(n, hq * hd), rtol=2 ** -6, atol=2 ** -6,
+                np.testing.assert_allclose(g, plain.attention(q, k, v, rnd=bf).reshape(n, hq * hd), rtol=2 ** -6, atol=2 ** -6,
                                            err_msg=f"prompt {i}")
     for a, b in zip(*runs):
         np.testing.assert_array_equal(a, b)

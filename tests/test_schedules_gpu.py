@@ -152,3 +152,39 @@ def test_more_single_token_sequences_than_a_captured_step_holds(tmp_path):
         for s in slots:
             engine.close(s)
         engine.check_status()
+
+
+def test_a_wait_that_runs_out_becomes_an_exception_and_the_engine_goes_on(tmp_path):
+    """Every wait of a kernel on a barrier is bounded; when one runs out the kernel sets a status word and returns, and
+    Engine.check_status() turns the word into an exception. Here a kernel whose only wait nothing can satisfy (a barrier
+    that expects bytes nobody sends) is given a limit of two milliseconds: it returns, the word is set, check_status
+    raises and clears it, and the next step gives the logits it gave before. Nothing faults and nothing hangs."""
+    import time
+
+    import torch
+    from abacus_b200.engine import Engine, load_model
+    from abacus_b200.kernels import ops
+    folder = folder_of(tmp_path, "D")
+    engine = Engine(load_model(folder, "bfloat16"), max_tokens=256)
+    tokens = random_tokens(np.random.default_rng(1), 70, TINY["D"]["cfg"]["vocab_size"])
+    slot = engine.open()
+    before = engine.step([(slot, tokens, [69])]).cpu().numpy()
+    engine.close(slot)
+    engine.check_status()
+    ops.set_wait_limit_ns(2_000_000)
+    try:
+        start = time.perf_counter()
+        ops.wait_that_runs_out(ops.kernel_status(torch.device("cuda", 0)))
+        torch.cuda.synchronize()
+        assert time.perf_counter() - start < 0.2  # two milliseconds, not the quarter of a second of the default
+    finally:
+        ops.set_wait_limit_ns(250_000_000)
+    with pytest.raises(RuntimeError, match="a wait that ran out"):
+        engine.check_status()
+    engine.check_status()  # the words were cleared
+    slot = engine.open()
+    again = engine.step([(slot, tokens, [69])]).cpu().numpy()
+    engine.close(slot)
+    engine.check_status()
+    assert np.array_equal(before, again)
+

@@ -4,8 +4,11 @@ This is the entry point for callers that cannot allocate device memory themselve
 whose whole GPU memory belongs to its own pool, a loop that cannot afford cudaMalloc's
 synchronisation, a plugin inside someone else's process): its scratch is an array inside the
 library. The test gives it inputs and an output it made itself, like such a caller would, and
-checks the result against abk_attention_decode, which takes its scratch as an argument, on two
-calls in a row that share the built-in array. The file's name makes pytest collect it last.
+checks the result on two calls in a row that share the built-in array: against plain attention
+over the keys and values gathered from the pages (an oracle that shares nothing with the kernel:
+windows, both page sizes' edges, the padding rows and the second call are all held to it), and,
+bit for bit, against abk_attention_decode, which takes its scratch as an argument. The file's name
+makes pytest collect it last.
 """
 import ctypes
 
@@ -47,6 +50,23 @@ def _call_noalloc(lib, qkv, out, batch, kv, window, max_positions, status):
         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
 
 
+def _plain_attention(qkv, lengths, kv, window):
+    """What plain attention gives for each sequence's last position, from the keys and values its pages hold
+    (sequence i sits in slot i: slots are handed out lowest first)."""
+    from plain import qwen3_plain as plain
+    k_pool, v_pool = kv.k.float().cpu().numpy(), kv.v.float().cpu().numpy()  # [pages, kv heads, 64, hd]
+    table = kv.page_table.cpu().numpy()
+    rows = []
+    for i, n in enumerate(lengths):
+        pages = table[i, :-(-n // 64)]
+        k = np.concatenate([k_pool[p] for p in pages], axis=1)[:, :n].transpose(1, 0, 2)  # [n, kv heads, hd]
+        v = np.concatenate([v_pool[p] for p in pages], axis=1)[:, :n].transpose(1, 0, 2)
+        q = np.zeros((n, HQ, HD), dtype=np.float32)  # only the last position's query is the row's
+        q[-1] = qkv[i, :HQ * HD].float().cpu().numpy().reshape(HQ, HD)
+        rows.append(plain.attention(q, k, v, window or None, rnd=plain.bf16_round)[-1].reshape(-1))
+    return np.stack(rows)
+
+
 def test_noalloc_entry_point_matches_the_one_with_a_scratch_argument():
     from abacus_b200.kernels import load_module, ops
     from abacus_b200.parts import Workspace
@@ -63,11 +83,34 @@ def test_noalloc_entry_point_matches_the_one_with_a_scratch_argument():
         rc = _call_noalloc(lib, qkv, got, batch, kv, window, batch.max_len_after, status)
         assert rc == 0, lib.abk_last_error().decode()
         torch.cuda.synchronize()
-        # same kernels, same order of summation: the tolerance of the kernel tests (2^-7) is far from needed
-        np.testing.assert_allclose(got.float().cpu().numpy(), want.float().cpu().numpy(), rtol=2 ** -7, atol=2 ** -7,
-                                   err_msg=f"call {call}")
+        # against plain attention, at the tolerance of the kernel tests: one bfloat16 rounding of the result
+        np.testing.assert_allclose(got[:len(lengths)].float().cpu().numpy(), _plain_attention(qkv, lengths, kv, window),
+                                   rtol=2 ** -7, atol=2 ** -7, err_msg=f"call {call}")
+        # and the same bits as the entry point that is given its scratch: same kernels, same order of summation
+        assert torch.equal(got, want), f"call {call}"
         assert float(got[len(lengths):].float().abs().sum()) == 0.0  # padding rows
     assert status.tolist() == [0, 0, 0, 0]
+
+
+def test_a_row_beyond_the_bound_is_reported_not_computed():
+    """max_positions sizes the grid; a row at or beyond it has no CTA for its last chunks. The kernel says so in the
+    status word, writes zeros for that row and leaves the tickets at zero, so that the next call finds them as it must."""
+    from abacus_b200.kernels import load_module
+    lib = load_module("attention_decode_static")
+    lengths = [300, 40]
+    cache, kv, batch, qkv = _setup(lengths, seed=4)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = torch.full((batch.n_rows, HQ * HD), 5.0, dtype=torch.bfloat16, device="cuda")
+    assert _call_noalloc(lib, qkv, out, batch, kv, 0, 256, status) == 0  # the first row is at position 299
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 2, 0]
+    assert float(out[0].float().abs().sum()) == 0.0
+    np.testing.assert_allclose(out[1:2].float().cpu().numpy(), _plain_attention(qkv, lengths, kv, 0)[1:2], rtol=2 ** -7, atol=2 ** -7)
+    status.zero_()
+    assert _call_noalloc(lib, qkv, out, batch, kv, 0, 320, status) == 0  # with the right bound all is well
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    np.testing.assert_allclose(out[:2].float().cpu().numpy(), _plain_attention(qkv, lengths, kv, 0), rtol=2 ** -7, atol=2 ** -7)
 
 
 def test_noalloc_entry_point_refuses_what_its_array_cannot_hold():
