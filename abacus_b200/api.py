@@ -18,6 +18,8 @@ from .engine.generate import Generator
 from .sampling import Sampler
 
 CHAT_TEMPLATE = "<|im_start|>user\n{}<|im_end|>\n<|im_start|>assistant\n<think>\n\n</think>\n\n"  # src/main.c:168
+DEFAULT_CONTEXT = 4096   # abacus caps a sequence at 4,096 tokens (src/model.c:15)
+DEFAULT_SEQUENCES = 8    # the cache's default room: this many sequences of that length
 
 
 class LM:
@@ -25,7 +27,7 @@ class LM:
         self.model = load_model(folder, dtype)
         spec = self.model.spec
         if max_tokens is None:
-            max_tokens = min(spec.max_positions, 4096) * 8  # src/model.c:15 caps a sequence at 4096
+            max_tokens = min(spec.max_positions, DEFAULT_CONTEXT) * DEFAULT_SEQUENCES
         self.engine = Engine(self.model, max_tokens=max_tokens, max_slots=max_slots, max_context=max_context)
         self.tokenizer = None
         if os.path.exists(os.path.join(folder, "tokenizer.json")):

@@ -102,13 +102,12 @@ def parse(argv):
 
 
 def info_line(model):
-    """abacus's --info line (src/main.c:143-145); tools/check.py:52-53 keys its rule on the weights= word."""
+    """abacus's --info line (src/main.c:143-145): the architecture says what it is called and which sizes it shows;
+    tools/check.py:52-53 keys its rule on the weights= word."""
     import torch
-    s = model.spec
-    m, f = s.layers[0].mixer, s.layers[0].ffn
+    from .config.registry import get_architecture
     weights = "f32" if model.ctx.dtype == torch.float32 else "bf16"
-    return (f"qwen3 dim={s.hidden} hidden={f.inter} layers={len(s.layers)} heads={m.n_heads}/{m.n_kv_heads} "
-            f"head_dim={m.head_dim} vocab={s.vocab} weights={weights} kernels=sm_100a")
+    return f"{get_architecture(model.spec.architecture).info(model.spec)} weights={weights} kernels=sm_100a"
 
 
 def dump_logits(lm, ids, start, chunk, path):

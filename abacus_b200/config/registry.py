@@ -4,6 +4,7 @@ An architecture is an object with
   name                    the string config.json carries
   parse_config(dict)      -> a typed configuration with .to_spec() -> ModelSpec
   tensor_names(spec)      -> how safetensors names map onto the parts (see models/qwen3.py)
+  info(spec)              -> the model's name and sizes in one line, for the command line's --info
 Adding an architecture is one call of `register_architecture`; nothing else in
 the package names a model.
 """

@@ -101,3 +101,8 @@ class ModelSpec:
     tied_head: bool
     max_positions: int
     stop_tokens: tuple = field(default_factory=tuple)
+    frame: str = "plain"  # how tokens become the stream and the stream logits (parts/frame.py)
+
+    @property
+    def kind(self):  # the frame is built from the model's spec
+        return self.frame

@@ -49,6 +49,16 @@ def load_model(folder, dtype="bfloat16", device=None):
 _ONE_TOKEN, _WANT_IT = np.zeros(1, dtype=np.int64), [0]
 
 
+def capturable(model):
+    """(single-token steps, steps of several tokens): whether the model's steps may be replayed from captured
+    graphs. A captured graph replays device work only: a part whose forward decides anything on the host from the
+    step's contents cannot be captured, and parts say so: `capturable = True` on every part for single-token
+    steps; for steps of several tokens also no mixer with `capturable_prompts = False`."""
+    parts = list(model.parts())
+    decode = all(getattr(part, "capturable", False) for part in parts)
+    return decode, decode and all(getattr(part, "capturable_prompts", True) for part in parts)
+
+
 class Engine:
     def __init__(self, model, max_tokens, max_slots=None, max_context=None, use_graphs=True):
         self.model = model
@@ -59,11 +69,9 @@ class Engine:
         self.max_context = self.cache.max_context
         model.prepare(self.max_context)
         self.vocab = spec.vocab
-        # A captured graph replays device work only: a part whose forward decides anything on the host
-        # from the step's contents cannot be captured. Parts say so with `capturable = True`.
-        capturable = all(getattr(part, "capturable", False) for b in model.blocks for part in b.parts().values())
-        self.graphs = DecodeGraphs(self) if use_graphs and capturable else None
-        prompts = use_graphs and capturable and os.environ.get("ABACUS_PROMPT_GRAPHS", "1") != "0"
+        decode_graphs, prompt_graphs = capturable(model)
+        self.graphs = DecodeGraphs(self) if use_graphs and decode_graphs else None
+        prompts = use_graphs and prompt_graphs and os.environ.get("ABACUS_PROMPT_GRAPHS", "1") != "0"
         self.prompt_graphs = PromptGraphs(self) if prompts else None
         self._step_batch = None
 
@@ -146,7 +154,7 @@ class Engine:
             grow = lambda n, least: max(least, 1 << max(0, int(n) - 1).bit_length())
             b = StepBatch(grow(max(n_rows, b.cap_rows if b else 0), 256), grow(max(n_seqs, b.cap_seqs if b else 0), 16),
                           grow(max(n_logits, b.cap_logits if b else 0), 64), self.model.ctx.device,
-                          attention_heads=self.model.attention_heads)
+                          plans=self.model.step_plans())
             self._step_batch = b
         return b
 

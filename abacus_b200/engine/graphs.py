@@ -14,7 +14,8 @@ A step that brings prompts is a few hundred launches too, each costing the host 
 microseconds: for a small model that is as long as the GPU works on them. Such steps are captured per
 (rows, sequences, wanted rows), each rounded up to a bucket, the second time a shape comes by (a
 shape seen once is not worth a capture); the step's work lists for the attention kernels travel in
-the StepBatch like its other indices, so a replay needs nothing from the host but that one copy.
+the StepBatch like its other indices, so a replay needs nothing from the host but that one copy. Whether a
+model's steps may be captured at all is the engine's question to the model's parts (engine.capturable).
 """
 import gc
 
@@ -38,7 +39,7 @@ class DecodeGraph:
         self.engine, self.rows, self.position_bound = engine, rows, position_bound
         device = engine.model.ctx.device
         self.batch = StepBatch(rows, rows if seqs is None else seqs, rows if logit_rows is None else logit_rows, device,
-                               attention_heads=engine.model.attention_heads)
+                               plans=engine.model.step_plans())
         self.batch.position_bound = position_bound
         self.graph = None
         self.generation = -1
@@ -130,8 +131,6 @@ class PromptGraphs:
         self.engine, self.keep = engine, keep
         self.graphs, self.seen = {}, {}
         self.captured = self.replayed = 0
-        needs = [n for n in engine.model.cache_needs() if n is not None]
-        self.windowed = any(getattr(n, "window", None) for n in needs)
 
     def key(self, sequences):
         rows = sum(len(s.tokens) for s in sequences)
@@ -140,8 +139,8 @@ class PromptGraphs:
 
     def takes(self, sequences):
         """Whether this step is replayed (or captured now). Steps of one token per sequence are the decode
-        graphs' (or run as they are); a model with a window checks its steps on the host."""
-        if self.windowed or all(len(s.tokens) == 1 for s in sequences):
+        graphs' (or run as they are)."""
+        if all(len(s.tokens) == 1 for s in sequences):
             return False
         key = self.key(sequences)
         if key in self.graphs:

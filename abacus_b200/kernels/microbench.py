@@ -136,7 +136,10 @@ def _attention_setup(batch, context, heads, kv_heads, head_dim, new_tokens):
         cache.reserve(slot, context)
         seqs.append(Sequence(slot, [0] * new_tokens, context - new_tokens, []))
     rows = batch * new_tokens
-    b = StepBatch(rows, batch, 0, "cuda", attention_heads=heads).fill(seqs)
+    from ..parts.attention_plan import AttentionLists, AttentionStepPlan
+    plan = AttentionStepPlan(heads)
+    b = StepBatch(rows, batch, 0, "cuda", plans=[plan]).fill(seqs)
+    b.lists = AttentionLists(b.plan[plan.name])
     qkv = torch.randn(rows, (heads + 2 * kv_heads) * head_dim, device="cuda").to(torch.bfloat16)
     out = torch.empty(rows, heads * head_dim, dtype=torch.bfloat16, device="cuda")
     return cache, kv, b, qkv, out
@@ -164,7 +167,7 @@ def bench_prefill_attention(args):
     ws = Workspace(torch.device("cuda", 0))
     scale = args.head_dim ** -0.5
     ops.qkv_prep(qkv, args.heads, args.kv_heads, args.head_dim, b, None, None, 0.0, None, None, 0, False, kv)
-    fn = lambda: ops.attention(qkv, out, args.heads, args.kv_heads, args.head_dim, scale, None, b, kv, ws=ws)
+    fn = lambda: ops.attention(qkv, out, args.heads, args.kv_heads, args.head_dim, scale, None, b, kv, ws=ws, lists=b.lists)
     us, best = timed_graph_flushed(fn)
     flops = args.batch * 4.0 * args.head_dim * args.heads * args.tokens * (args.tokens + 1) / 2
     return {"kernel": "attention (prefill)", "batch": args.batch, "tokens": args.tokens, "us": round(us, 2),

@@ -295,15 +295,16 @@ def sample_all(logits, temperature, rng_state, out, n_rows=None, rng_index=None)
                                    _p(rng_state), _p(rng_index), _p(out), _p(sums), _stream()), "sample_all", kernels=2)
 
 
-def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, ws=None):
+def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, ws=None, lists=None):
     """Attention of a step: picks the kernel for the phase and sizes; every case the faster kernels
-    do not take goes to the general one."""
+    do not take goes to the general one. lists: the step's tiles and work list for the prefill kernels
+    (parts/attention_plan.py: AttentionLists); without them a step of several tokens runs on the general kernel."""
     if (batch.is_decode and not from_step and ws is not None and qkv.dtype == torch.bfloat16
             and attention_decode_takes(n_heads, n_kv_heads, head_dim, cache)):
         attention_decode(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws)
-    elif (not batch.is_decode and not from_step and not window and qkv.dtype == torch.bfloat16
+    elif (not batch.is_decode and not from_step and not window and qkv.dtype == torch.bfloat16 and lists is not None
           and attention_prefill_takes(head_dim, cache)):
-        attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cache)
+        attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cache, lists)
     else:
         attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=from_step)
 
@@ -315,9 +316,10 @@ def attention_prefill_takes(head_dim, cache):
     return head_dim in (64, 128) and cache.tokens_per_page == 64 and cache.ring_pages == 0
 
 
-def attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cache):
+def attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cache, lists):
     """Causal attention of whole prompts (or any several tokens per sequence) against the paged bfloat16
-    cache, on the tensor cores, tiles of 64 query rows (src/model.c:197-211). No window."""
+    cache, on the tensor cores (src/model.c:197-211). No window. lists: the step's tiles of query rows and the
+    work list of the kernel that halves long tiles (parts/attention_plan.py)."""
     _need_cuda(qkv, out)
     n = batch.n_rows
     row = (n_heads + 2 * n_kv_heads) * head_dim
@@ -327,19 +329,19 @@ def attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cac
     pool_rows = cache.k.shape[0] * cache.k.shape[1] * cache.k.shape[2]
     if head_dim == 128 and not PREFILL_ON_MMA:  # tcgen05: tiles of 128 query rows, scores and output in tensor memory
         lib = load_module("attention_tc")
-        work = batch.work  # what each CTA does: whole tiles, long tiles twice (engine/batch.py)
+        work = lists.work  # what each CTA does: whole tiles, long tiles twice
         sc = _Scratch.of(qkv.device)
         room = sc.attention_halves_pairs // n_heads
-        if batch.n_halved > room:
-            raise KernelRefused(f"attention_prefill_tc: the step halves {batch.n_halved} tiles, its scratch memory holds "
-                                f"{room} for {n_heads} heads (the StepBatch was made for {batch.attention_heads})")
+        if lists.n_halved > room:
+            raise KernelRefused(f"attention_prefill_tc: the step halves {lists.n_halved} tiles, its scratch memory holds "
+                                f"{room} for {n_heads} heads (the lists were made for another number of heads)")
         _check(lib, lib.abk_attention_prefill_tc(
             _p(qkv), _ll(row), _i(n), _p(out), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _p(work),
             _i(work.shape[0]), _i(room), _p(sc.attention_halves), _p(sc.attention_halves_tickets), _p(cache.k), _p(cache.v), _ll(pool_rows), _p(cache.page_table), _i(cache.table_width),
             _i(cache.tokens_per_page), _p(kernel_status(qkv.device)), _stream()), "attention_prefill_tc")
         return
     lib = load_module("attention_mma")
-    tiles = batch.query_tiles(64)
+    tiles = lists.tiles(64)
     _check(lib, lib.abk_attention_prefill(
         _p(qkv), _ll(row), _i(n), _p(out), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _p(tiles),
         _i(tiles.shape[0]), _p(batch.seq_start), _p(batch.seq_pos0), _p(batch.seq_len_after), _p(batch.seq_slot),
@@ -465,7 +467,7 @@ class _Scratch:
     def argmax_tickets(self):
         return self._lazy("argmax_tickets", lambda: guards.zeros(self.argmax_rows, torch.int32, self.device, what="tickets of argmax"))
 
-    attention_halves_pairs = 384  # (tile, head) pairs the prefill attention may halve in one launch (engine/batch.py)
+    attention_halves_pairs = 384  # (tile, head) pairs the prefill attention may halve in one launch (parts/attention_plan.py)
 
     @property
     def attention_halves(self):

@@ -35,6 +35,12 @@ class Qwen3Architecture:
         return ModelLayout(embed="model.embed_tokens.weight", final_norm="model.norm.weight", head="lm_head.weight",
                            layers=layers)
 
+    def info(self, spec):
+        """The model's name and sizes as abacus's --info prints them (src/main.c:143-145)."""
+        m, f = spec.layers[0].mixer, spec.layers[0].ffn
+        return (f"qwen3 dim={spec.hidden} hidden={f.inter} layers={len(spec.layers)} heads={m.n_heads}/{m.n_kv_heads} "
+                f"head_dim={m.head_dim} vocab={spec.vocab}")
+
     def tensor_names(self, spec, available=None):
         return expected_tensors(spec, self.layout(spec), available)
 

@@ -1,6 +1,6 @@
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, BuildContext, Registry
+from .base import BLOCKS, FEED_FORWARDS, FRAMES, MIXERS, NORMS, POSITIONS, BuildContext, Registry
 from .workspace import Workspace
 from .linear import Linear
-from . import attention, block, mlp, norm, position  # noqa: F401  (register the built-in parts)
+from . import attention, block, frame, mlp, norm, position  # noqa: F401  (register the built-in parts)
 
-__all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "BuildContext", "Registry", "Workspace", "Linear"]
+__all__ = ["BLOCKS", "FEED_FORWARDS", "FRAMES", "MIXERS", "NORMS", "POSITIONS", "BuildContext", "Registry", "Workspace", "Linear"]

@@ -8,6 +8,7 @@ import torch
 
 from ..cache.need import CacheNeed
 from ..kernels import ops
+from .attention_plan import AttentionLists, AttentionStepPlan
 from .base import MIXERS, POSITIONS, to_device
 from .linear import Linear
 
@@ -25,6 +26,18 @@ class Attention:
         self.position = POSITIONS.build(s.position) if s.position is not None else None
         self.q_size, self.kv_size = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
         self.cos = self.sin = None
+        # a step of several tokens of a windowed layer is checked on the host (it may have to be refused): such
+        # steps cannot be replayed from a captured graph; single-token steps can
+        self.capturable_prompts = s.window is None
+        self.lists = AttentionStepPlan(s.n_heads)  # the prefill kernels' tiles and work list, made per step
+
+    def step_plans(self):
+        """What this mixer wants made on the host for every step and sent with the step's indices."""
+        return [self.lists]
+
+    def step_weights(self):
+        """The tensors a step reads once whatever its size (for the bytes a decode step must move)."""
+        return [self.qkv_proj.weight, self.o_proj.weight, self.q_norm, self.k_norm]
 
     def param_shapes(self):
         s = self.spec
@@ -71,7 +84,8 @@ class Attention:
         if from_step and (batch.any_continuation or not writes):
             raise ops.KernelRefused("windowed attention takes several tokens of a sequence only at its start, "
                                     "and only with keys of its own")
+        mine = batch.plan.get(self.lists.name)
         ops.attention(qkv, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, batch, cache.kv,
-                      from_step=from_step, ws=ws)
+                      from_step=from_step, ws=ws, lists=AttentionLists(mine) if mine is not None else None)
         self.o_proj.forward(att, out, n)
         return out

@@ -27,6 +27,11 @@ Interfaces (duck-typed; these base classes only document them):
   all do are replayed as CUDA graphs. Without it the model runs step by step.
   Block.forward(x, y, batch, cache, ws) -> y': runs norms, mixer and
       feed-forward in its arrangement; y is the output still to be added to x.
+  Frame: see parts/frame.py.
+  Optional, on any part:
+    step_weights() -> tensors the part reads once per step whatever the step's size (the bytes a decode step moves)
+    capturable_prompts (mixers): False if steps of several tokens must not be replayed from a captured graph
+    step_plans() (mixers): see engine/batch.py
 """
 from dataclasses import dataclass
 
@@ -65,6 +70,7 @@ POSITIONS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 BLOCKS = Registry("block arrangement")
+FRAMES = Registry("frame (embedding, last norm and output matrix)")
 
 
 def to_device(t, ctx, dtype=None):

@@ -35,6 +35,9 @@ class GatedMLP:
         self.gate_up = Linear(to_device(stacked.reshape(2 * inter, -1).contiguous(), ctx, ctx.dtype))
         self.down = Linear(to_device(params["down"], ctx, ctx.dtype))
 
+    def step_weights(self):
+        return [self.gate_up.weight, self.down.weight]
+
     def forward(self, xn, out, batch, ws):
         n, inter = batch.n_rows, self.spec.inter
         act = ws.get("act", (n, inter), self.ctx.dtype)

@@ -19,6 +19,9 @@ class RMSNorm:
     def bind(self, params, ctx):
         self.weight = to_device(params["weight"], ctx, torch.float32)
 
+    def step_weights(self):
+        return [self.weight]
+
     def forward(self, x, y, out, rows=None, n_rows=None):
         ops.add_rmsnorm(x, y, self.weight, out, self.spec.eps, rows=rows, n_rows=n_rows)
         return out

@@ -13,7 +13,6 @@ Two tiny configurations are used: A, and B with its vocabulary padded from 389 t
 groups of 3, a head size decoupled from the width, eps 1e-5, norm weights that are not 1). Every matrix
 of these has rows % 8 == 0 and cols % 32 == 0, which the int8 engine needs (src/matmul.c:100-103).
 """
-import hashlib
 import json
 import os
 import subprocess
@@ -25,7 +24,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
-from helpers import TINY, make_model_folder  # noqa: E402
+from helpers import TINY, make_model_folder, weights_digest  # noqa: E402
 
 CASES = {"A": (7, 17), "B392": (8, 40)}  # configuration -> (seed of the token ids, how many)
 
@@ -52,8 +51,7 @@ def main():
                             "--from", "1", "--chunk", "0"], check=True)  # src/main.c:85-102: positions >= from - 1
             logits = np.fromfile(dump, dtype="<f4").reshape(len(ids), vocab)
             info = subprocess.run([exe, model_bin, "--info"], check=True, capture_output=True, text=True).stdout.strip()
-            with open(os.path.join(folder, "model.safetensors"), "rb") as f:
-                digest = hashlib.sha256(f.read()).hexdigest()
+            digest = weights_digest(folder)
             np.save(os.path.join(HERE, f"tiny{name}_abacus.npy"), logits.astype(np.float32))
             with open(os.path.join(HERE, f"tiny{name}_abacus.json"), "w") as f:
                 json.dump({"ids": ids, "info": info, "weights_sha256": digest, "config": name}, f)

@@ -68,6 +68,16 @@ def make_model_folder(tmp, name, scales=SHARP):
     return folder
 
 
+def weights_digest(folder):
+    """A hash of a model folder's tensors by name, whatever order the file keeps them in."""
+    import hashlib
+    from plain import qwen3_plain as plain
+    h = hashlib.sha256()
+    for name, t in sorted(plain.read_safetensors(os.path.join(folder, "model.safetensors")).items()):
+        h.update(name.encode() + str(t.shape).encode() + np.ascontiguousarray(t).tobytes())
+    return h.hexdigest()
+
+
 def random_tokens(rng, n, vocab):
     return [int(t) for t in rng.integers(0, vocab, n)]
 

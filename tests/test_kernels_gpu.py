@@ -273,7 +273,10 @@ class Harness:
             ss.append(Sequence(slot, [0] * n, self.cache.length[slot], []))
             self.cache.reserve(slot, self.cache.length[slot] + n)
         rows = sum(n for _, n in seqs)
-        batch = self.last_batch = StepBatch(rows + 3, len(seqs) + 1, 0, "cuda").fill(ss)  # three padding rows at the end
+        from abacus_b200.parts.attention_plan import AttentionLists, AttentionStepPlan
+        plan = AttentionStepPlan(self.hq)
+        batch = self.last_batch = StepBatch(rows + 3, len(seqs) + 1, 0, "cuda", plans=[plan]).fill(ss)  # three padding rows at the end
+        lists = self.last_lists = AttentionLists(batch.plan[plan.name])
         pad = np.full((3, qkv.shape[1]), 7.0, dtype=np.float32)
         q = dev(np.concatenate([qkv, pad]), self.dtype)
         kv = self.cache.views[0].kv
@@ -289,7 +292,7 @@ class Harness:
             from abacus_b200.parts import Workspace
             self.ws = getattr(self, "ws", None) or Workspace(torch.device("cuda", 0))
             ops.attention(q, out, self.hq, self.hkv, self.hd, scale, self.window, batch, kv, from_step=from_step,
-                          ws=self.ws)
+                          ws=self.ws, lists=lists)
         for slot, n in seqs:
             self.cache.advance(slot, n)
         if general or all(n == 1 for _, n in seqs):
@@ -606,9 +609,9 @@ def test_prefill_attention_halves_long_tiles(ops):
         slots = [h.cache.open_slot() for _ in data]
         first = [data[0], data[1][:500], data[2]]
         _, got1 = h.step(ops, [(s, len(d)) for s, d in zip(slots, first)], np.concatenate(first), *none, general=False)
-        assert h.last_batch.n_halved == 4  # the tiles from row 384 on of the prompts of 700 and of 500 tokens
+        assert h.last_lists.n_halved == 4  # the tiles from row 384 on of the prompts of 700 and of 500 tokens
         _, got2 = h.step(ops, [(slots[1], 300)], data[1][500:], *none, general=False)
-        assert h.last_batch.n_halved == 3
+        assert h.last_lists.n_halved == 3
         got = [got1[:700], np.concatenate([got1[700:1200], got2]), got1[1200:]]
         runs.append(got)
         if run == 0:

@@ -333,11 +333,38 @@ class RunningMeanSpec:
     kind: str = "toy_running_mean"
 
 
+class TokensSoFar:
+    """The toy mixer's step plan (engine/batch.py): for every row of the step, how many tokens its sequence holds up
+    to and including it. Made on the host from the step's sequences, carried to the device with the step's indices."""
+    name = "toy_tokens_so_far"
+
+    class Layout:
+        def __init__(self, n_rows):
+            self.words = n_rows
+
+    def layout(self, n_rows, n_seqs):
+        return self.Layout(n_rows)
+
+    def fill(self, layout, sequences, words, is_decode, exact):
+        words[:] = 1  # padding rows divide by one
+        row = 0
+        for s in sequences:
+            n = len(s.tokens)
+            words[row:row + n] = np.arange(s.start + 1, s.start + n + 1)
+            row += n
+        return row
+
+
 class RunningMean:
-    """out_t = W . mean(xn_0..xn_t): the state per sequence is the running sum (fixed size, no keys)."""
+    """out_t = W . mean(xn_0..xn_t): the state per sequence is the running sum (fixed size, no keys); the divisors
+    come from a step plan of its own."""
+    counts = TokensSoFar()
 
     def __init__(self, spec):
         self.spec = spec
+
+    def step_plans(self):
+        return [self.counts]
 
     def param_shapes(self):
         return {"w": (self.spec.hidden, self.spec.hidden)}
@@ -350,12 +377,14 @@ class RunningMean:
         return CacheNeed(state_shape=(self.spec.hidden,))
 
     def forward(self, xn, out, batch, cache, ws):
+        mine = batch.plan[self.counts.name]
+        assert mine.info == batch.n_tokens  # what the plan's fill returned comes back with its words
+        so_far = mine.words.float()[:, None]
         row = 0
         for s in batch.sequences:  # a ragged step: walk each sequence's rows from its own state
             n = len(s.tokens)
             cum = cache.state[s.slot] + torch.cumsum(xn[row:row + n].float(), dim=0)
-            counts = torch.arange(s.start + 1, s.start + n + 1, device=xn.device, dtype=torch.float32)[:, None]
-            out[row:row + n] = (cum / counts) @ self.w.T
+            out[row:row + n] = (cum / so_far[row:row + n]) @ self.w.T
             cache.state[s.slot] = cum[-1]
             row += n
         return out
@@ -400,6 +429,8 @@ def test_a_toy_mixer_is_registered_built_and_stepped(tmp_path):
     model = Model(spec, layout, tensors, torch.float32, torch.device("cuda", 0))
     engine = Engine(model, max_tokens=64 * 4)
     assert sorted(engine.cache.states) == [0, 2] and len(engine.cache.groups) == 1
+    # the step carries the toy mixer's plan beside the attention layer's, each once
+    assert sorted(p.name for p in model.step_plans()) == ["attention_lists_3", "toy_tokens_so_far"]
 
     def plain_toy(ids):
         w = {k: v.float().numpy() for k, v in tensors.items()}

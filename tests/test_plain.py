@@ -6,7 +6,7 @@ import os
 import numpy as np
 import pytest
 
-from helpers import TINY, log_softmax64, make_model_folder
+from helpers import TINY, log_softmax64, make_model_folder, weights_digest
 from plain import qwen3_plain as plain
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
@@ -26,8 +26,7 @@ def test_plain_matches_abacus_engine(tmp_path, name):
     meta = json.load(open(os.path.join(GOLDEN, f"tiny{name}_abacus.json")))
     golden = np.load(os.path.join(GOLDEN, f"tiny{name}_abacus.npy"))
     folder = make_model_folder(tmp_path, name)
-    digest = hashlib.sha256(open(os.path.join(folder, "model.safetensors"), "rb").read()).hexdigest()
-    assert digest == meta["weights_sha256"], "the random weights are not the ones the golden logits were made with"
+    assert weights_digest(folder) == meta["weights_sha256"], "the random weights are not the ones the golden logits were made with"
     cfg, w = plain.load(folder)
     got = plain.forward(cfg, w, meta["ids"])
     assert got.shape == golden.shape

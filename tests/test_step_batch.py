@@ -1,10 +1,15 @@
-"""The index arrays of a step (engine/batch.py), on the CPU: rows, padding, the tiles and the work list that the
-prefill attention kernels walk. The kernels trust these lists; what they must hold is checked here against a
-reconstruction from the sequences alone."""
+"""The index arrays of a step (engine/batch.py), on the CPU: rows and padding; a step plan's words travelling with
+them; and the attention mixer's own plan (parts/attention_plan.py), the tiles and the work list that its prefill
+kernels walk. The kernels trust these lists; what they must hold is checked here against a reconstruction from the
+sequences alone."""
 import numpy as np
 import pytest
 
-from abacus_b200.engine.batch import CTA_SLOTS, HALVED_PAIRS, PAIRED_ROWS, TILE_ROWS, WORK_INTS, Sequence, StepBatch
+from abacus_b200.engine.batch import Sequence, StepBatch
+from abacus_b200.parts.attention_plan import (HALVED_PAIRS, PAIRED_ROWS, TILE_ROWS, WORK_INTS, AttentionLists,
+                                              AttentionStepPlan)
+
+CTA_SLOTS = 2 * 148  # the places the tests give the tile-halving kernel: two CTAs on each of a B200's SMs
 
 
 def random_step(rng, n_seqs, longest):
@@ -53,10 +58,47 @@ def test_a_step_that_does_not_fit_or_wants_a_place_it_does_not_bring_is_refused(
 
 
 def test_a_decode_step_has_no_tiles():
-    b = StepBatch(8, 8, 8, "cpu").fill([Sequence(i, [7], 100 + i, [0]) for i in range(5)])
-    assert b.is_decode and set(b.work.reshape(-1).tolist()) == {-1}
+    plan = AttentionStepPlan(4, cta_slots=CTA_SLOTS)
+    b = StepBatch(8, 8, 8, "cpu", plans=[plan]).fill([Sequence(i, [7], 100 + i, [0]) for i in range(5)])
+    lists = AttentionLists(b.plan[plan.name])
+    assert b.is_decode and set(lists.work.reshape(-1).tolist()) == {-1} and lists.n_halved == 0
     for r in TILE_ROWS:
-        assert set(getattr(b, f"tiles{r}").tolist()) == {-1}
+        assert set(lists.tiles(r).reshape(-1).tolist()) == {-1}
+
+
+class CountingPlan:
+    """A step plan of a toy mixer: for every sequence, how many tokens it brings and where it starts."""
+    name = "counting"
+
+    class Layout:
+        def __init__(self, n_seqs):
+            self.words = 2 * n_seqs
+
+    def layout(self, n_rows, n_seqs):
+        return self.Layout(n_seqs)
+
+    def fill(self, layout, sequences, words, is_decode, exact):
+        words[:] = -7
+        for i, s in enumerate(sequences):
+            words[2 * i], words[2 * i + 1] = len(s.tokens), s.start
+        return {"sequences": len(sequences), "decode": is_decode}
+
+
+def test_a_step_plan_travels_with_the_step():
+    """The engine knows nothing of what a plan holds: it gives the plan its words in the step's one buffer, at a fixed
+    place, and hands the mixer what the plan returned."""
+    counting, lists = CountingPlan(), AttentionStepPlan(2, cta_slots=CTA_SLOTS)
+    b = StepBatch(300, 4, 4, "cpu", plans=[counting, lists, counting])  # the same name twice: one part of the buffer
+    assert list(b.plans) == ["counting", lists.name]
+    seqs = [Sequence(3, [1] * 200, 0, [199]), Sequence(1, [2] * 5, 64, [])]
+    b.fill(seqs)
+    view = b.plan["counting"]
+    assert view.words.tolist() == [200, 0, 5, 64, -7, -7, -7, -7] and view.info == {"sequences": 2, "decode": False}
+    at = view.words.data_ptr()
+    b.fill([Sequence(0, [9], 10, [0])])
+    assert b.plan["counting"].words.data_ptr() == at and b.plan["counting"].words.tolist()[:2] == [1, 10]
+    assert b.plan["counting"].info["decode"] and b.tokens[:1].tolist() == [9]
+    assert (b._dev == b._host).all()  # the plans' words went to the device in the step's own copy
 
 
 def expected_tiles(seqs, rows_per_tile):
@@ -76,16 +118,18 @@ def test_tiles_and_work_list_cover_every_row_once(heads):
         if all(len(s.tokens) == 1 for s in seqs):
             continue
         rows = sum(len(s.tokens) for s in seqs)
-        b = StepBatch(rows + 5, len(seqs) + 1, 16, "cpu", attention_heads=heads).fill(seqs)
+        plan = AttentionStepPlan(heads, cta_slots=CTA_SLOTS)
+        b = StepBatch(rows + 5, len(seqs) + 1, 16, "cpu", plans=[plan]).fill(seqs)
+        lists = AttentionLists(b.plan[plan.name])
         for r in TILE_ROWS:
-            tiles = b.query_tiles(r).numpy()
+            tiles = lists.tiles(r).numpy()
             real = tiles[tiles[:, 0] >= 0]
             assert len(real) == len(expected_tiles(seqs, r)) == len({tuple(t) for t in real.tolist()})
             assert {tuple(t) for t in real.tolist()} == expected_tiles(seqs, r)
             assert (tiles[len(real):] == -1).all()  # padding behind, never between
             seen = [seqs[i].start + r0 for i, r0 in real.tolist()]
             assert seen == sorted(seen, reverse=True)  # the tiles that see the most keys first
-        work = b.work.numpy()
+        work = lists.work.numpy()
         real = work[work[:, 0] >= 0]
         assert (work[len(real):] == -1).all() and work.shape[1] == WORK_INTS
         first_row = np.cumsum([0] + [len(s.tokens) for s in seqs])
@@ -106,7 +150,7 @@ def test_tiles_and_work_list_cover_every_row_once(heads):
                 assert sorted(p for p, _ in ps) == [1, 2] and ps[0][1] == ps[1][1]
                 assert pages_seen(seqs[seq], r0, PAIRED_ROWS) >= 8
                 ids.append(ps[0][1])
-        assert sorted(ids) == list(range(len(ids))) and b.n_halved == len(ids)
+        assert sorted(ids) == list(range(len(ids))) and lists.n_halved == len(ids)
         assert len(ids) * heads <= HALVED_PAIRS  # what the kernel has scratch memory for
         if ids:
             halved_somewhere = True
@@ -128,29 +172,48 @@ def test_buckets_of_captured_steps():
         assert prompt_bucket(b) == b  # a bucket is its own bucket
 
 
-class FakeNeed:
-    def __init__(self, window):
-        self.window = window
-
-
 class FakeContext:
     device = "cpu"
 
 
+class FakePart:
+    def __init__(self, **flags):
+        self.__dict__.update(flags)
+
+
 class FakeModel:
-    ctx, attention_heads = FakeContext(), 4
+    ctx = FakeContext()
 
-    def __init__(self, window=None):
-        self.window = window
+    def __init__(self, parts=()):
+        self._parts = list(parts)
 
-    def cache_needs(self):
-        return [FakeNeed(None), None, FakeNeed(self.window)]
+    def parts(self):
+        return iter(self._parts)
+
+    def step_plans(self):
+        return []
 
 
 class FakeEngine:
-    def __init__(self, window=None):
-        self.model = FakeModel(window)
+    def __init__(self):
+        self.model = FakeModel()
         self.max_context = 4096
+
+
+def test_which_models_are_captured():
+    """A model's steps are replayed from graphs only if every part says that its forward pass launches device work
+    alone; steps of several tokens also only if no mixer objects (a windowed attention layer does: it checks such steps
+    on the host)."""
+    from abacus_b200.engine.engine import capturable
+    sure = FakePart(capturable=True)
+    assert capturable(FakeModel([sure, sure])) == (True, True)
+    assert capturable(FakeModel([sure, FakePart()])) == (False, False)  # a part that does not say so is not
+    assert capturable(FakeModel([sure, FakePart(capturable=True, capturable_prompts=False)])) == (True, False)
+    from abacus_b200.config.specs import AttentionSpec
+    from abacus_b200.parts import MIXERS
+    spec = dict(hidden=32, n_heads=2, n_kv_heads=1, head_dim=16, scale=0.25, qk_norm_eps=None, position=None)
+    assert MIXERS.build(AttentionSpec(**spec)).capturable_prompts
+    assert not MIXERS.build(AttentionSpec(**spec, window=24)).capturable_prompts
 
 
 def test_which_steps_are_captured():
@@ -165,8 +228,6 @@ def test_which_steps_are_captured():
     assert graphs.key(same_shape) == graphs.key(prompts) == (768, 2, 2)
     other = [Sequence(3, [2] * 650, 0, [0, 1, 2]), Sequence(4, [2] * 90, 0, [1])]
     assert graphs.key(other) == (768, 2, 4) and not graphs.takes(other)
-    assert not PromptGraphs(FakeEngine(window=24)).takes(prompts)  # a window: steps are checked on the host
-    assert not PromptGraphs(FakeEngine(window=24)).takes(prompts)
     d = DecodeGraphs(FakeEngine())
     assert d.takes(decode) and not d.takes(prompts)
     assert not d.takes([Sequence(0, [5], 3, [])])  # a decode row whose logits nobody wants is not the captured shape
