@@ -17,6 +17,7 @@ from ..config.registry import load_config
 from ..models.model import Model
 from ..weights.loader import load_folder
 from .batch import Sequence, StepBatch
+from .cstep import CStep
 from .graphs import DecodeGraphs, PromptGraphs
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -69,6 +70,8 @@ class Engine:
         self.max_context = self.cache.max_context
         model.prepare(self.max_context)
         self.vocab = spec.vocab
+        # the step function in C where the model is made of the library's own parts, else the parts' forward()
+        self.cstep = CStep(model, self.cache) if CStep.serves(model) else None
         decode_graphs, prompt_graphs = capturable(model)
         self.graphs = DecodeGraphs(self) if use_graphs and decode_graphs else None
         prompts = use_graphs and prompt_graphs and os.environ.get("ABACUS_PROMPT_GRAPHS", "1") != "0"
@@ -122,11 +125,17 @@ class Engine:
         else:
             batch = self._room_for(sum(len(s.tokens) for s in seqs), len(seqs), sum(len(s.want) for s in seqs))
             batch.fill(seqs, exact=True)
-            logits = self.model.forward(batch, self.cache)
+            logits = self.forward(batch)
             self.last_batch = batch
         for s in seqs:
             self.cache.advance(s.slot, len(s.tokens))
         return logits
+
+    def forward(self, batch):
+        """The model's forward pass over a filled step: in one call to C where that serves the model."""
+        if self.cstep is not None:
+            return self.cstep.run(batch)
+        return self.model.forward(batch, self.cache)
 
     def step_ahead(self, slots, tokens_dev):
         """A decode step (one token per sequence, its logits wanted) whose tokens are on the device, for instance

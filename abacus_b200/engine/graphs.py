@@ -46,13 +46,13 @@ class DecodeGraph:
         self.logits = None
 
     def capture(self, sequences):
-        model, cache = self.engine.model, self.engine.cache
+        model = self.engine.model
         self.batch.fill(sequences, pad_logits=True)
         # once outside a capture: loads the kernel libraries, sets function attributes, sizes the workspace
         side = torch.cuda.Stream(device=model.ctx.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            model.forward(self.batch, cache)
+            self.engine.forward(self.batch)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         from ..kernels import ops
@@ -64,7 +64,7 @@ class DecodeGraph:
         gc.disable()
         try:
             with torch.cuda.graph(self.graph):
-                self.logits = model.forward(self.batch, cache)
+                self.logits = self.engine.forward(self.batch)
         finally:
             if collecting:
                 gc.enable()

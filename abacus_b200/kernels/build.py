@@ -24,7 +24,7 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 MODULES = ("elementwise", "gemm_simt", "gemm_tc", "attention_generic", "attention_decode", "attention_mma", "gemm_rows",
-           "sampling", "attention_decode_static", "attention_decode_ring", "attention_tc", "utility")
+           "sampling", "attention_decode_static", "attention_decode_ring", "attention_tc", "utility", "step")
 
 
 # ABACUS_TRACE=1 builds every library with the launch-timeline records of csrc/common.cuh compiled in

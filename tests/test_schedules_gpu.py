@@ -10,6 +10,7 @@ import sys
 
 import numpy as np
 import pytest
+import torch
 
 from helpers import ROOT, SHARP, TINY, assert_logits, random_tokens
 from plain import qwen3_plain as plain
@@ -41,8 +42,8 @@ def test_command_line_text_tokenize_and_bench(tmp_path):
     stops = sorted(set(tok.stop_ids()) | {459})
     exe = [sys.executable, os.path.join(ROOT, "bin", "abacus"), folder, "--fp32"]
 
-    def run(*args):
-        done = subprocess.run([*exe, *args], check=True, capture_output=True)
+    def run(*args, env=None):
+        done = subprocess.run([*exe, *args], check=True, capture_output=True, env=env)
         return done.stdout.decode("utf-8", errors="replace"), done.stderr.decode()
 
     text = "Why is the sea salty?"
@@ -58,6 +59,11 @@ def test_command_line_text_tokenize_and_bench(tmp_path):
     assert run("-p", text, "--temp", "0.9", "--seed", "11", "-n", "10")[0] == tok.decode(want)
     out, _ = run("--tokenize", "It's 2026, and the engine writes <|im_end|> tokens.")
     assert [int(t) for t in out.split()] == tok.encode("It's 2026, and the engine writes <|im_end|> tokens.")
+    # the switches: no captured prompt steps, no captured steps' C walker; the same ids either way
+    ids = " ".join(str(t) for t in tok.encode(CHAT_TEMPLATE.format(text)))
+    plain_ids = " ".join(str(t) for t in plain.generate(cfg, w, [int(t) for t in ids.split()], 9))
+    for switch in ({}, {"ABACUS_PROMPT_GRAPHS": "0"}, {"ABACUS_C_STEP": "0"}, {"ABACUS_PROMPT_GRAPHS": "0", "ABACUS_C_STEP": "0"}):
+        assert run("--ids", ids, "-n", "9", env=dict(os.environ, **switch))[0].strip() == plain_ids, switch
     res = json.loads(run("--bench", "64", "8", "--batch", "3")[0])
     assert res["pp"] == 64 and res["tg"] == 8 and res["batch"] == 3 and res["prefill_tok_s"] > 0 and res["decode_tok_s"] > 0
 
@@ -187,4 +193,52 @@ def test_a_wait_that_runs_out_becomes_an_exception_and_the_engine_goes_on(tmp_pa
     engine.close(slot)
     engine.check_status()
     assert np.array_equal(before, again)
+
+
+@pytest.mark.parametrize("name, dtype", [("B", "float32"), ("C", "float32"), ("C2", "bfloat16"), ("D", "bfloat16"), ("A", "bfloat16")])
+def test_the_step_function_in_c_launches_what_the_parts_would(tmp_path, name, dtype):
+    """A step is one call to the C walker (csrc/step.cu) where the model is made of the library's own parts, and a walk
+    through the parts' forward() otherwise. Both must pick the same kernels with the same arguments: prompts of unequal
+    lengths, a continuation by several tokens and decode steps give the same bits either way, with and without
+    captured graphs. (A windowed layer refuses the continuation on both ways, with the same words.)"""
+    from abacus_b200.engine import Engine, load_model
+    from abacus_b200.kernels import ops
+    folder = folder_of(tmp_path, name)
+    model = load_model(folder, dtype)
+    rng = np.random.default_rng(4)
+    vocab = TINY[name]["cfg"]["vocab_size"]
+    prompts = [random_tokens(rng, n, vocab) for n in (70, 3, 131)]
+    more = [random_tokens(rng, n, vocab) for n in (9, 2, 1)]
+    windowed = any(t == "sliding_attention" for t in TINY[name]["cfg"].get("layer_types", []))
+
+    def run(engine):
+        out, slots = [], [engine.open() for _ in prompts]  # (a step's logits live in the workspace: copied at once)
+        out.append(engine.step([(s, p, [0, len(p) - 1]) for s, p in zip(slots, prompts)]).clone())
+        try:
+            out.append(engine.step([(s, m, list(range(len(m)))) for s, m in zip(slots, more)]).clone())
+        except ops.KernelRefused as e:
+            assert windowed and "windowed attention" in str(e)
+            for s in slots:  # what the refused step reserved stays reserved: start over in fresh slots
+                engine.close(s)
+            slots = [engine.open() for _ in prompts]
+            out.append(engine.step([(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)]).clone())
+        for k in range(3):
+            out.append(engine.step([(s, [int(t)], [0]) for s, t in zip(slots, rng_tokens[k])]).clone())
+        for s in slots:
+            engine.close(s)
+        engine.check_status()
+        return out
+
+    rng_tokens = [random_tokens(rng, 3, vocab) for _ in range(3)]
+    results = []
+    for use_graphs in (False, True):
+        for c_step in (True, False):
+            engine = Engine(model, max_tokens=64 * 9, use_graphs=use_graphs)
+            assert engine.cstep is not None
+            if not c_step:
+                engine.cstep = None
+            results.append(run(engine) + (run(engine) if use_graphs else []))  # twice: the second time from captured graphs
+    for other in results[1:]:
+        for a, b in zip(results[0], other):
+            assert torch.equal(a, b)
 
