@@ -427,6 +427,195 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_persistent_kernel(const 
     }
 }
 
+// ------------------------------------------------------------------ pairs of CTAs on tiles of 256 rows
+// The persistent kernel above is bound by the operands' way from the L2 into shared memory: a CTA brings 128 rows of x
+// and BN rows of w for every block of K. Here two CTAs of a cluster (the two SMs of a pair) work on one tile of 256 rows:
+// each brings its 128 rows of x and only half of the tile's rows of w, and one tcgen05.mma.cta_group::2 of the even CTA
+// multiplies what both hold, each CTA's tensor memory getting its 128 rows of the result. Per FLOP a CTA loads
+// (128 + BN / 2) / (128 + BN) of what it loaded alone: two thirds at BN = 256. Every load is the CTA's own plain TMA copy
+// into its own shared memory; there is no multicast. Roles as above (warp 0 loads, warp 1 of the leader multiplies, warps
+// 2-5 of both store); the leader's `full` barriers count the bytes of both CTAs, its commits reach both CTAs' `empty` and
+// `acc_full` barriers, and the peer's storing warps report to the leader's `acc_empty`.
+// ABACUS_GEMM_PAIRS=0 keeps every product on single CTAs (for comparison).
+static bool abk_pairs_off() {
+    static int off = -1;
+    if (off < 0) {
+        const char *e = getenv("ABACUS_GEMM_PAIRS");
+        off = e && e[0] == '0';
+    }
+    return off != 0;
+}
+
+template <int BN, int STAGES> struct PairSmem {
+    static constexpr int A_BYTES = TILE_P * TILE_K * 2, B_BYTES = (BN / 2) * TILE_K * 2;
+    static constexpr int BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /* alignment */ + 256 /* barriers */;
+};
+
+template <int BN, int STAGES, typename TO, bool GATED = false>
+__global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p,
+                                                                    const __grid_constant__ CUtensorMap map_q, GemmTc g,
+                                                                    int m_tiles, int tiles) {
+    using S = PairSmem<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *a_tiles = smem, *b_tiles = smem + STAGES * S::A_BYTES;
+    uint64_t *full = (uint64_t *)(smem + STAGES * (S::A_BYTES + S::B_BYTES));
+    uint64_t *empty = full + STAGES, *acc_full = empty + STAGES, *acc_empty = acc_full + 2;
+    uint32_t *tmem_holder = (uint32_t *)(acc_empty + 2);
+    volatile int *flags = (volatile int *)(tmem_holder + 1);  // [0]: a wait ran out
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)tc::cluster_rank();  // 0: the leader, 1: its peer
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) tc::mbar_init(&full[s], 1), tc::mbar_init(&empty[s], 1);
+        for (int b = 0; b < 2; b++) tc::mbar_init(&acc_full[b], 1), tc::mbar_init(&acc_empty[b], 8);  // four warps of each CTA
+        flags[0] = 0;
+        tc::mbar_init_fence();
+        tc::tma_prefetch_map(&map_p), tc::tma_prefetch_map(&map_q);
+    }
+    if (warp == 1) tc::tmem_alloc_pair(tmem_holder, TMEM_COLS);
+    tc::fence_before_sync();
+    tc::cluster_sync();  // both CTAs' barriers are there before either signals the other's
+    tc::fence_after_sync();
+    const uint32_t tmem = *tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // A stage is full when both CTAs' copies have landed: all of them report to the leader's barrier.
+            constexpr uint32_t STAGE_BYTES = 2 * (S::A_BYTES + S::B_BYTES);
+            const int ahead = min(STAGES, g.k_blocks);
+            // the weights of the first tile's first stages are asked for before pdl_wait(): nobody writes them
+            for (int i = 0; i < ahead; i++) {
+                if (rank == 0) tc::mbar_expect_tx(&full[i], STAGE_BYTES);
+                tc::tma_load_2d_pair(b_tiles + i * S::B_BYTES, &map_q, i * TILE_K, (pair / m_tiles) * BN + rank * (BN / 2),
+                                     tc::peer_smem(tc::smem_addr(&full[i]), 0));
+            }
+            pdl_wait();
+            int issued = 0;
+            for (int t = pair; t < tiles && !flags[0]; t += pairs) {
+                const int p0 = (t % m_tiles) * (2 * TILE_P) + rank * TILE_P, q0 = (t / m_tiles) * BN + rank * (BN / 2);
+                for (int kb = 0; kb < g.k_blocks; kb++, issued++) {
+                    const int s = issued % STAGES;
+                    const uint32_t bar = tc::peer_smem(tc::smem_addr(&full[s]), 0);
+                    if (issued >= ahead) {
+                        if (!tc::mbar_wait(&empty[s], ((issued / STAGES) & 1) ^ 1)) {  // (its own: the commit reaches both)
+                            flags[0] = 1;
+                            break;
+                        }
+                        if (rank == 0) tc::mbar_expect_tx(&full[s], STAGE_BYTES);
+                        tc::tma_load_2d_pair(b_tiles + s * S::B_BYTES, &map_q, kb * TILE_K, q0, bar);
+                    }
+                    tc::tma_load_2d_pair(a_tiles + s * S::A_BYTES, &map_p, kb * TILE_K, p0, bar);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = tc::idesc_bf16_f32(2 * TILE_P, BN);
+            int done = 0, it = 0;
+            for (int t = pair; t < tiles && !flags[0]; t += pairs, it++) {
+                const int b = it & 1;
+                if (!tc::mbar_wait(&acc_empty[b], ((it >> 1) & 1) ^ 1)) {  // both CTAs are done with this accumulator
+                    flags[0] = 1;
+                    break;
+                }
+                tc::fence_after_sync();
+                for (int kb = 0; kb < g.k_blocks; kb++, done++) {
+                    const int s = done % STAGES;
+                    if (!tc::mbar_wait(&full[s], (done / STAGES) & 1)) {
+                        flags[0] = 1;
+                        break;
+                    }
+                    tc::fence_after_sync();
+                    const uint32_t a = tc::smem_addr(a_tiles + s * S::A_BYTES), bq = tc::smem_addr(b_tiles + s * S::B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TILE_K / 16; k++)
+                        tc::mma_ss_pair(tmem + b * BN, tc::smem_desc_k_sw128(a + k * 32), tc::smem_desc_k_sw128(bq + k * 32),
+                                        idesc, kb > 0 || k > 0);
+                    tc::mma_commit_pair(&empty[s]);
+                }
+                if (flags[0]) break;
+                tc::mma_commit_pair(&acc_full[b]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3, row = quarter * 32 + lane;
+        TO *out = (TO *)g.out;
+        int it = 0;
+        pdl_wait();
+        for (int t = pair; t < tiles; t += pairs, it++) {
+            const int b = it & 1;
+            const int p = (t % m_tiles) * (2 * TILE_P) + rank * TILE_P + row, q0 = (t / m_tiles) * BN;
+            const bool ok = __all_sync(0xffffffffu, !flags[0] && tc::mbar_wait(&acc_full[b], (it >> 1) & 1));
+            if (!ok) {
+                flags[0] = 1;
+                break;
+            }
+            tc::fence_after_sync();
+            if constexpr (GATED) {
+                const int f0 = (t / m_tiles) * (BN / 2);  // the tile's first feature
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+                    uint32_t gv[32], uv[32];
+                    tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c0, gv);
+                    tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c0 + 16, gv + 16);
+                    tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + BN / 2 + c0, uv);
+                    tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + BN / 2 + c0 + 16, uv + 16);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float gate = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gv[j])));
+                        const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(uv[j])));
+                        gv[j] = __float_as_uint(silu_mul_fast(gate, up));
+                    }
+                    if (p < g.P && f0 + c0 + 32 <= g.Q) {
+                        store16(out + (long long)p * g.stride_p + f0 + c0, gv);
+                        store16(out + (long long)p * g.stride_p + f0 + c0 + 16, gv + 16);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c0, v);
+                    tc::tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c0 + 16, v + 16);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int h = 0; h < 32; h += 16) {
+                        if (g.vec && p < g.P && q0 + c0 + h + 16 <= g.Q) {
+                            store16(out + (long long)p * g.stride_p + q0 + c0 + h, v + h);
+                        } else if (p < g.P) {
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                if (q0 + c0 + h + j < g.Q)
+                                    out[(long long)p * g.stride_p + (long long)(q0 + c0 + h + j) * g.stride_q] =
+                                        from_float<TO>(__uint_as_float(v[h + j]));
+                        }
+                    }
+                }
+            }
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive_in_cluster(tc::peer_smem(tc::smem_addr(&acc_empty[b]), 0));
+        }
+    }
+    // Nobody leaves while the other CTA may still signal its barriers or write its tensor memory. (After a wait that ran
+    // out, copies may still be on their way into this CTA's shared memory: give them a tenth of a millisecond.)
+    if (flags[0]) {
+        const uint64_t t0 = tc::global_ns();
+        while (tc::global_ns() - t0 < 100000) __nanosleep(1000);
+    }
+    tc::fence_before_sync();
+    tc::cluster_sync();
+    if (flags[0] && threadIdx.x == 0) atomicOr(g.status + 1, 1);
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_free_pair(tmem, TMEM_COLS);
+    }
+}
+
 // ------------------------------------------------------------------ host side
 
 typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -498,6 +687,23 @@ static int launch(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g,
     return ABK_LAUNCH_RESULT();
 }
 
+// The kernel for pairs of CTAs: m_tiles and tiles count tiles of 256 rows; one cluster of two CTAs per pair of SMs.
+template <int BN, int STAGES, typename TO, bool GATED = false>
+static int launch_pair(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g, int m_tiles, int tiles, cudaStream_t s) {
+    auto kernel = gemm_tc_pair_kernel<BN, STAGES, TO, GATED>;
+    constexpr int bytes = PairSmem<BN, STAGES>::BYTES;
+    if (cudaError_t e = abk_allow_shared_memory((const void *)kernel, bytes)) return (int)e;  // once per device
+    const int pairs = abk_sm_count() / 2;
+    abk_launch_clusters(kernel, dim3(2 * (tiles < pairs ? tiles : pairs)), dim3(GEMM_THREADS), (size_t)bytes, s, 2, mp, mq, g,
+                        m_tiles, tiles);
+    return ABK_LAUNCH_RESULT();
+}
+// Whether a product of many rows goes to the pairs: enough tiles of 256 x 256 to give most pairs of SMs one.
+static bool pairs_win(int M, int N) {
+    const long long tiles = (long long)((M + 2 * TILE_P - 1) / (2 * TILE_P)) * ((N + 255) / 256);
+    return M > 256 && N >= 256 && tiles >= (abk_sm_count() / 2) * 6 / 7;
+}
+
 template <int BN, int STAGES, typename TO>
 static int launch_persistent(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g, int m_tiles, int tiles,
                              cudaStream_t s) {
@@ -524,6 +730,13 @@ extern "C" int abk_gemm_tc_swiglu(const void *x, const void *w, void *act, int M
     g.out = act, g.P = M, g.Q = N, g.K = K, g.stride_p = ldo, g.stride_q = 1;
     g.k_blocks = (K + TILE_K - 1) / TILE_K, g.k_blocks_per_split = g.k_blocks, g.splits = 1;
     g.partials = nullptr, g.tickets = nullptr, g.status = status, g.vec = 1, g.in_cluster = 0, g.weights_are_p = 0;
+    if (pairs_win(M, 2 * N) && !abk_pairs_off()) {
+        CUtensorMap mw_half;
+        rc = tensor_map(w, 2LL * N, K, ldw, 128, &mw_half);
+        if (rc) return rc;
+        const int m_tiles2 = (M + 2 * TILE_P - 1) / (2 * TILE_P);
+        return launch_pair<256, 6, __nv_bfloat16, true>(mx, mw_half, g, m_tiles2, m_tiles2 * (N / 128), (cudaStream_t)stream);
+    }
     const int m_tiles = (M + TILE_P - 1) / TILE_P, tiles = m_tiles * (N / 128);
     auto kernel = gemm_tc_persistent_kernel<256, 4, __nv_bfloat16, true>;
     constexpr int bytes = GemmSmem<256, 4>::BYTES;
@@ -574,6 +787,22 @@ extern "C" int abk_gemm_tc(const void *x, const void *w, void *out, int out_dtyp
     bool persistent = !swap && M > 256 && N >= 128 && K <= 4096 &&
                       (long long)((M + TILE_P - 1) / TILE_P) * ((N + 127) / 128) >= 96;
     if (force_persistent >= 0) persistent = force_persistent != 0 && !swap;
+    // many tiles of 256 x 256: pairs of CTAs (force_persistent 2 pins them, for tests), whatever the length of K
+    const bool pair = !swap && !force_bn && (force_persistent == 2 || (force_persistent < 0 && pairs_win(M, N) && !abk_pairs_off()));
+    if (pair) {
+        CUtensorMap mx2, mw2;
+        int rc2 = tensor_map(x, M, K, ldx, TILE_P, &mx2);
+        if (!rc2) rc2 = tensor_map(w, N, K, ldw, 128, &mw2);
+        if (rc2) return rc2;
+        GemmTc g2;
+        g2.out = out, g2.P = M, g2.Q = N, g2.K = K, g2.stride_p = ldo, g2.stride_q = 1;
+        g2.k_blocks = (K + TILE_K - 1) / TILE_K, g2.k_blocks_per_split = g2.k_blocks, g2.splits = 1;
+        g2.partials = nullptr, g2.tickets = nullptr, g2.status = status, g2.in_cluster = 0, g2.weights_are_p = 0;
+        g2.vec = ((uintptr_t)out % 16 == 0) && (ldo * (out_dtype == ABK_BF16 ? 2 : 4)) % 16 == 0;
+        const int m_tiles2 = (M + 2 * TILE_P - 1) / (2 * TILE_P), tiles2 = m_tiles2 * ((N + 255) / 256);
+        return out_dtype == ABK_BF16 ? launch_pair<256, 6, __nv_bfloat16>(mx2, mw2, g2, m_tiles2, tiles2, (cudaStream_t)stream)
+                                     : launch_pair<256, 6, float>(mx2, mw2, g2, m_tiles2, tiles2, (cudaStream_t)stream);
+    }
     if (persistent && !force_bn) bn = (long long)((M + TILE_P - 1) / TILE_P) * ((N + 255) / 256) >= 112 ? 256 : 128;
     if (persistent && bn != 128 && bn != 256) ABK_REFUSE("gemm_tc: the persistent kernel has column tiles of 128 and 256, not %d", bn);
     int P = swap ? N : M, Q = swap ? M : N;

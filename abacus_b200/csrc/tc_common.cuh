@@ -158,6 +158,53 @@ __device__ __forceinline__ void mma_commit(uint64_t *bar) {
                  : "memory");
 }
 
+// ------------------------------------------------------------------ pairs of CTAs on one tile (cta_group::2)
+// Two CTAs of a cluster (ranks 2i and 2i + 1, on the two SMs of a pair) share one product: each holds half of A's
+// rows and half of B's rows in its own shared memory, at the same offsets, and gets its half of the accumulator's rows
+// in its own tensor memory; the even CTA (the leader) issues the instruction for both. Every load is a CTA's own,
+// plain copy into its own shared memory (no multicast); only its completion is reported to the leader's barrier.
+//
+// Both CTAs allocate together: one warp of each, the same warp in both, the same `holder` offset.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *holder, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(holder)),
+                 "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free_pair(uint32_t addr, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(columns) : "memory");
+}
+// A CTA's own box into its own shared memory; the bytes are reported to the barrier at `bar_in_cluster`, an address
+// in the cluster's window (peer_smem of the leader's barrier).
+__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, int x, int y, uint32_t bar_in_cluster) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_addr(dst)), "l"((uint64_t)map), "r"(bar_in_cluster), "r"(x), "r"(y)
+        : "memory");
+}
+// D[tensor memory of both CTAs] (+)= A . B^T over the pair: M = 256 (128 rows from each CTA), N columns (N / 2 rows of B
+// from each CTA). Issued by one thread of the leader.
+__device__ __forceinline__ void mma_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+// The barrier at this offset in both CTAs of the pair gets one arrival when all tcgen05.mma issued so far are done.
+__device__ __forceinline__ void mma_commit_pair(uint64_t *bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_addr(bar)),
+        "h"((uint16_t)3)
+        : "memory");
+}
+// One arrival on a barrier of another CTA of the cluster.
+__device__ __forceinline__ void mbar_arrive_in_cluster(uint32_t bar_in_cluster) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_in_cluster) : "memory");
+}
+
 // ------------------------------------------------------------------ tcgen05.ld
 // 32 lanes x 16 columns of 32 bits: thread t of the warp gets lane (base lane + t), v[j] = column j.
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *v) {

@@ -146,8 +146,15 @@ def device_decode(model, prompts, steps, warmup, context=CONTEXT, with_clocks=Fa
     slots = [engine.open() for _ in range(batch)]
     logits = engine.step([(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
     first = sampler.sample(logits, None).tolist()
-    logits = engine.step([(s, [t], [0]) for s, t in zip(slots, first)])  # captures the graph
-    graph = engine.graphs.get(engine.plan([(s, [0], [0]) for s in slots]))
+    # The graph of the loop's step: captured for a bound on the positions that holds to the loop's end, so that no
+    # row outgrows it on the way (a decode graph's grid is sized for its bound).
+    from abacus_b200.engine import Sequence
+    seqs = engine.plan([(s, [t], [0]) for s, t in zip(slots, first)])
+    last = max(len(p) for p in prompts) + warmup + steps + 2
+    graph = engine.graphs.get([Sequence(q.slot, q.tokens, last - 1, q.want) for q in seqs])
+    logits = graph.run(seqs)
+    for s in slots:
+        engine.cache.advance(s, 1)
     tokens = graph.batch.tokens[:batch]
     sampler.sample(logits, None, out=tokens)
 

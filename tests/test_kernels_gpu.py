@@ -493,6 +493,20 @@ def test_gemm_tc_persistent_kernel(ops, out_dtype):
     assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
 
 
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tc_pairs_of_ctas(ops, out_dtype):
+    """The kernel in which two CTAs of a cluster share a tile of 256 rows (tcgen05.mma.cta_group::2, every CTA loading
+    its own halves): fewer tiles than pairs of SMs and so many that a pair walks several and both accumulators come
+    round; ragged edges in M, N and K, among them a last tile of rows that only the leader's half reaches and a last
+    tile of columns that only the leader's half of the weights reaches; a K shorter than the ring of stages and one
+    far longer."""
+    rng = np.random.default_rng(29)
+    for m, n, k in [(300, 520, 72), (1300, 3600, 136), (2048, 1024, 1032), (257, 256, 8), (120, 100, 64), (2048, 4096, 1024),
+                    (600, 2560, 9728)]:
+        _gemm_case(ops, m, n, k, out_dtype, rng, persistent=2)
+    assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
+
+
 @pytest.mark.parametrize("m, n, k", [(1, 128, 64), (1, 1024, 2048), (8, 4096, 1024), (64, 1000, 72), (65, 192, 96),
                                       (300, 389, 96), (2048, 1024, 1024), (5, 151936, 128), (130, 70, 8), (1500, 4096, 264),
                                       # the down projections of the 4B and 8B shapes: K beyond the persistent kernel's 4,096
