@@ -130,11 +130,15 @@ __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bflo
                 if (token < M && n0 + row < N) {
                     float sum = part[0][row][token];
                     const uint32_t at = (uint32_t)__cvta_generic_to_shared(&part[0][row][token]);
-                    for (int c = 1; c < ranks; c++) {
-                        float v;
-                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(tc::peer_smem(at, c)));
-                        sum += v;
+                    // the other CTAs' sums: all loads in flight before the first is added (in the CTAs' order)
+                    float v[8];
+#pragma unroll
+                    for (int c = 1; c < 8; c++) {
+                        v[c] = 0.0f;
+                        if (c < ranks) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[c]) : "r"(tc::peer_smem(at, c)));
                     }
+#pragma unroll
+                    for (int c = 1; c < 8; c++) sum += v[c];
                     out[(long long)token * ldo + n0 + row] = from_float<TO>(sum);
                 }
             }

@@ -235,11 +235,15 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
             const uint32_t base = tc::smem_addr((float *)smem + row * (BN + 4));
             TO *out = (TO *)g.out;
             for (int gi = split * per; gi < min(groups, (split + 1) * per); gi++) {
-                float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                for (int s0 = 0; s0 < g.splits; s0++) {
-                    const float4 t = tc::ld_cluster_f4(tc::peer_smem(base + gi * 16, s0));
-                    sum.x += t.x, sum.y += t.y, sum.z += t.z, sum.w += t.w;
-                }
+                // all splits' loads are in flight before the first sum (a warp issues in order: a sum right behind
+                // its load would wait out every round trip through the cluster one after the other)
+                float4 t[8];
+#pragma unroll
+                for (int s0 = 0; s0 < 8; s0++)
+                    t[s0] = s0 < g.splits ? tc::ld_cluster_f4(tc::peer_smem(base + gi * 16, s0)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                float4 sum = t[0];
+#pragma unroll
+                for (int s0 = 1; s0 < 8; s0++) sum.x += t[s0].x, sum.y += t[s0].y, sum.z += t[s0].z, sum.w += t[s0].w;
                 const float r4[4] = {sum.x, sum.y, sum.z, sum.w};
                 if (p < g.P) {
 #pragma unroll

@@ -157,7 +157,8 @@ def swiglu(gate_up):
     """silu(gate) * up with rows laid out [gate | up] (src/model.c:274-282)."""
     inter = gate_up.shape[-1] // 2
     g, u = gate_up[..., :inter], gate_up[..., inter:]
-    return (g / (F32(1.0) + np.exp(-g, dtype=F32)) * u).astype(F32)
+    with np.errstate(over="ignore"):  # exp(-g) may be inf for a very negative gate: g / inf is the 0 that is meant
+        return (g / (F32(1.0) + np.exp(-g, dtype=F32)) * u).astype(F32)
 
 
 # ----------------------------------------------------------------- the model
