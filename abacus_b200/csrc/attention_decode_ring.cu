@@ -15,11 +15,20 @@
 //
 // A row's result depends on S, that is on the size of the batch, only in the order of float32
 // sums. Formula: src/model.c:197-211.
+//
+// The kernel may also take the step between the q/k/v product and attention into itself (src/model.c:247-259: the
+// per-head norm of q and k, their rotary encoding, the new token's key and value into the cache): a launch less in
+// every layer of a decode step. Every CTA of a cluster then prepares the group's query heads for itself, into shared
+// memory; the CTA that holds the new token's page prepares its key and value as well, writes them to the cache, and
+// the warp whose 16 keys include the new token puts them into the page's copy in shared memory once that has landed
+// (the copy may have read the page before or after the write: either way the row is then the new one). The
+// arithmetic is that of the preparation's own kernel (qkv_prep.cuh), so the result is the same to the bit.
 #define ABK_DEFINE_ERROR
 #include "common.cuh"
 #include "tc_common.cuh"
 #include "tensor_map.cuh"
 #include "mma_tiles.cuh"
+#include "qkv_prep.cuh"
 
 #define RING_MAX_STAGES 12
 #define RING_STAGE_BYTES (96 * 1024)  // keys and values in flight per CTA when an SM holds two
@@ -37,6 +46,13 @@ struct AttnDecodeRing {
     PagedCache cache;
     int stages;  // depth of the ring
     int *status;
+    // prepare != 0: q, and the new token's k and v beside it in the row (k head h at q + (n_heads + h) * head_dim, v head h
+    // n_kv_heads heads further), are as the product left them, and are prepared here
+    int prepare;
+    const float *q_norm, *k_norm;  // null: no norm
+    float eps;
+    const float *cos, *sin;  // [positions, head_dim / 2]; null: no rotation
+    __nv_bfloat16 *k_pool, *v_pool;  // where the new key and value are kept; null: nowhere (the cache is another layer's)
 };
 
 template <int HD>
@@ -53,6 +69,7 @@ __global__ void __launch_bounds__(RING_THREADS) attn_decode_ring_kernel(const __
     float *cta_ml = cta_o + group * HD;                   // [group][2]: maximum (in units of log2) and sum
     float *warp_o = cta_ml + group * 2;                   // [4 warps][group][HD]
     float *warp_ml = warp_o + 4 * group * HD;             // [4 warps][group][2]
+    __nv_bfloat16 *q_s = (__nv_bfloat16 *)(((uintptr_t)(warp_ml + 4 * group * 2) + 15) & ~(uintptr_t)15);  // [group][HD]: the prepared query heads
     __shared__ uint64_t full[RING_MAX_STAGES], empty[RING_MAX_STAGES];
     __shared__ int failed;
 
@@ -83,6 +100,18 @@ __global__ void __launch_bounds__(RING_THREADS) attn_decode_ring_kernel(const __
         tc::mbar_init_fence();
     }
     __syncthreads();
+    // the lane's part in preparing heads: 8 elements of one of the 32 * 8 / HD heads a warp holds at a time
+    constexpr int LPH = HD / 8, HPW = 32 / LPH;
+    const int sub = lane / LPH, l = lane % LPH;
+    const bool upper = l >= LPH / 2;
+    float cs[8], sn[8];
+    if (p.prepare && warp != 4 && mine > 0 && p.cos) {  // the angles of the new token's position: nobody's output
+        const int at = (upper ? l - LPH / 2 : l) * 8;
+        const float4 *c4 = (const float4 *)(p.cos + (long long)pos * (HD / 2) + at), *s4 = (const float4 *)(p.sin + (long long)pos * (HD / 2) + at);
+        const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+        cs[0] = c0.x, cs[1] = c0.y, cs[2] = c0.z, cs[3] = c0.w, cs[4] = c1.x, cs[5] = c1.y, cs[6] = c1.z, cs[7] = c1.w;
+        sn[0] = s0.x, sn[1] = s0.y, sn[2] = s0.z, sn[3] = s0.w, sn[4] = s1.x, sn[5] = s1.y, sn[6] = s1.z, sn[7] = s1.w;
+    }
     if (warp != 4) pdl_wait();
 
     if (warp == 4) {
@@ -101,7 +130,9 @@ __global__ void __launch_bounds__(RING_THREADS) attn_decode_ring_kernel(const __
             for (int i = 0; i < n && go; i++, issued++) {
                 const int y = __shfl_sync(0xffffffffu, y_lane, i);
                 int bad = 0;
-                if (first_page + split + issued * splits == last_page) pdl_wait();  // the new token's page
+                // the new token's page: the kernel before this one may still be writing it, unless the new token
+                // is written here (then the page holds earlier steps' tokens, and the new row is put in after the copy)
+                if (!p.prepare && first_page + split + issued * splits == last_page) pdl_wait();
                 if (lane == 0) {
                     const int s = issued % stages;
                     if (!tc::mbar_wait(&empty[s], ((issued / stages) & 1) ^ 1)) {
@@ -126,9 +157,33 @@ __global__ void __launch_bounds__(RING_THREADS) attn_decode_ring_kernel(const __
         }
     } else if (mine > 0) {
         const int g_lo = lane >> 2, g_hi = g_lo + 8;  // this thread's two rows: query heads of the group
+        // the new token's key and value, held by the warp whose 16 keys include it in the CTA that has its page
+        const bool has_new = p.prepare && (last_page - first_page) % splits == split && (pos % PAGE) / 16 == warp;
+        uint4 new_kv = make_uint4(0, 0, 0, 0);  // lanes of head 0: the key's elements 8 l .., of head 1: the value's
+        if (p.prepare) {
+            const __nv_bfloat16 *row = p.q + (long long)r * p.q_row + l * 8;
+            for (int g0 = warp * HPW; g0 < group; g0 += 4 * HPW) {  // (the same for a whole warp)
+                const int g = g0 + sub;
+                const uint4 raw = g < group ? *(const uint4 *)(row + (long long)(kvh * group + g) * HD) : make_uint4(0, 0, 0, 0);
+                const uint4 done = prep_head_values<HD>(raw, true, p.q_norm, p.eps, p.cos != nullptr, l, upper, cs, sn);
+                if (g < group) *(uint4 *)(q_s + g * HD + l * 8) = done;
+            }
+            if (has_new) {
+                const long long head = sub == 0 ? p.n_heads + kvh : p.n_heads + p.n_kv_heads + kvh;
+                const uint4 raw = sub < 2 ? *(const uint4 *)(row + head * HD) : make_uint4(0, 0, 0, 0);
+                new_kv = prep_head_values<HD>(raw, sub == 0, p.k_norm, p.eps, p.cos != nullptr, l, upper, cs, sn);
+                if (sub < 2 && p.k_pool) {
+                    const int page = cache_page(p.cache, p.seq_slot[seq], pos);
+                    __nv_bfloat16 *pool = sub == 0 ? p.k_pool : p.v_pool;
+                    *(uint4 *)(pool + cache_offset(p.cache, page, kvh, p.n_kv_heads, pos, HD) + l * 8) = new_kv;
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // the four warps that multiply: all heads are in q_s
+        }
         uint32_t qf[HD / 16][4];
         {
-            const __nv_bfloat16 *q_lo = p.q + (long long)r * p.q_row + (long long)(kvh * group + g_lo) * HD + 2 * (lane & 3);
+            const __nv_bfloat16 *q_lo = p.prepare ? q_s + g_lo * HD + 2 * (lane & 3)
+                                                  : p.q + (long long)r * p.q_row + (long long)(kvh * group + g_lo) * HD + 2 * (lane & 3);
             const __nv_bfloat16 *q_hi = q_lo + 8 * HD;
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ks++) {
@@ -150,6 +205,13 @@ __global__ void __launch_bounds__(RING_THREADS) attn_decode_ring_kernel(const __
                 break;
             }
             const int j0 = pg * PAGE + 16 * warp;  // this warp's 16 keys of the page
+            if (has_new && pg == last_page) {  // the new token's row of the page's copy (only this warp reads it)
+                if (sub < 2) {
+                    uint8_t *tile = (sub == 0 ? k_s : v_s) + s * TILE_BYTES + (l / 8) * BOX_BYTES;
+                    *(uint4 *)(tile + sw128(0, pos % PAGE, l % 8)) = new_kv;
+                }
+                __syncwarp();
+            }
             if (j0 <= pos && j0 + 16 > lo) {
                 float sc[2][4];
                 scores<HD, 2>(sc, qf, tc::smem_addr(k_s + s * TILE_BYTES), 16 * warp, lane);
@@ -278,14 +340,16 @@ static int resident_clusters(int splits, int smem) {
     return clusters;
 }
 
-// max_positions: no row's position reaches it (with the number of rows it fixes the grid; a captured graph
-// passes its bound). status word 2 is set if a wait ran out.
-extern "C" int abk_attention_decode_ring(const void *q, long long q_row, void *out, int n_rows, int n_heads,
-                                         int n_kv_heads, int head_dim, float scale, int window, const int *token_seq,
-                                         const int *token_pos, const int *seq_slot, const void *k_pool,
-                                         const void *v_pool, long long pool_rows, const int *page_table, int table_width,
-                                         int ring_pages, int tokens_per_page, int max_positions, int *status,
-                                         void *stream) {
+struct RingPrepare {  // what the kernel needs to prepare q, k and v itself
+    const float *q_norm, *k_norm, *cos, *sin;
+    float eps;
+    int keep;  // the new key and value go to the cache (not where the cache is another layer's)
+};
+static int ring_launch(const void *q, long long q_row, void *out, int n_rows, int n_heads, int n_kv_heads, int head_dim,
+                       float scale, int window, const int *token_seq, const int *token_pos, const int *seq_slot,
+                       const void *k_pool, const void *v_pool, long long pool_rows, const int *page_table, int table_width,
+                       int ring_pages, int tokens_per_page, int max_positions, int *status, const RingPrepare *prepare,
+                       void *stream) {
     if (n_rows <= 0) return 0;
     if (head_dim != 64 && head_dim != 128) ABK_REFUSE("attention_decode_ring: head_dim %d is not 64 or 128", head_dim);
     if (tokens_per_page != PAGE) ABK_REFUSE("attention_decode_ring: pages of %d tokens, not %d", tokens_per_page, PAGE);
@@ -293,6 +357,9 @@ extern "C" int abk_attention_decode_ring(const void *q, long long q_row, void *o
         ABK_REFUSE("attention_decode_ring: %d heads in %d groups (at most 16 to a group)", n_heads, n_kv_heads);
     if (n_kv_heads > 65535 || n_rows > 65535) ABK_REFUSE("attention_decode_ring: %d rows or %d kv heads exceed a grid", n_rows, n_kv_heads);
     if (((uintptr_t)q & 3) || (q_row & 1)) ABK_REFUSE("attention_decode_ring: q must be 4-byte aligned");
+    if (prepare && ((((uintptr_t)q | (uintptr_t)prepare->q_norm | (uintptr_t)prepare->k_norm | (uintptr_t)prepare->cos |
+                      (uintptr_t)prepare->sin | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) || (q_row & 7) || !prepare->cos != !prepare->sin))
+        ABK_REFUSE("attention_decode_ring: rows, norms, angles and pools must be 16-byte aligned to be prepared here");
     if ((uintptr_t)out & 7) ABK_REFUSE("attention_decode_ring: out must be 8-byte aligned");
     CUtensorMap km, vm;
     int rc = tmap::bf16_rows_of_128_bytes(k_pool, pool_rows, head_dim, head_dim, PAGE, &km);
@@ -305,6 +372,11 @@ extern "C" int abk_attention_decode_ring(const void *q, long long q_row, void *o
     p.token_seq = token_seq, p.token_pos = token_pos, p.seq_slot = seq_slot;
     p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = ring_pages;
     p.cache.tokens_per_page = tokens_per_page;
+    p.prepare = prepare != nullptr;
+    p.q_norm = prepare ? prepare->q_norm : nullptr, p.k_norm = prepare ? prepare->k_norm : nullptr;
+    p.cos = prepare ? prepare->cos : nullptr, p.sin = prepare ? prepare->sin : nullptr, p.eps = prepare ? prepare->eps : 0.0f;
+    p.k_pool = prepare && prepare->keep ? (__nv_bfloat16 *)k_pool : nullptr;
+    p.v_pool = prepare && prepare->keep ? (__nv_bfloat16 *)v_pool : nullptr;
     {   // once per device
         cudaError_t e = abk_allow_shared_memory((const void *)attn_decode_ring_kernel<64>, 224 * 1024);
         if (e == cudaSuccess) e = abk_allow_shared_memory((const void *)attn_decode_ring_kernel<128>, 224 * 1024);
@@ -316,7 +388,8 @@ extern "C" int abk_attention_decode_ring(const void *q, long long q_row, void *o
     const long long pairs = (long long)n_rows * n_kv_heads;
     const int pages = (max_positions + PAGE - 1) / PAGE;
     const int tile_pair = 2 * PAGE * head_dim * 2;
-    const int fold_bytes = 5 * group * (head_dim + 2) * 4 + 1024 + 64;  // partial results, and room to align the ring
+    // partial results, the prepared query heads, and room to align them and the ring
+    const int fold_bytes = 5 * group * (head_dim + 2) * 4 + group * head_dim * 2 + 16 + 1024 + 64;
     int stages = RING_STAGE_BYTES / tile_pair;
     if (stages > (224 * 1024 - fold_bytes) / tile_pair) stages = (224 * 1024 - fold_bytes) / tile_pair;
     if (stages < 2) ABK_REFUSE("attention_decode_ring: a group of %d heads of %d leaves no room for a ring", group, head_dim);
@@ -344,4 +417,34 @@ extern "C" int abk_attention_decode_ring(const void *q, long long q_row, void *o
     if (head_dim == 64) cudaLaunchKernelEx(&cfg, attn_decode_ring_kernel<64>, km, vm, p);
     else cudaLaunchKernelEx(&cfg, attn_decode_ring_kernel<128>, km, vm, p);
     return ABK_LAUNCH_RESULT();
+}
+
+// max_positions: no row's position reaches it (with the number of rows it fixes the grid; a captured graph
+// passes its bound). status word 2 is set if a wait ran out.
+extern "C" int abk_attention_decode_ring(const void *q, long long q_row, void *out, int n_rows, int n_heads,
+                                         int n_kv_heads, int head_dim, float scale, int window, const int *token_seq,
+                                         const int *token_pos, const int *seq_slot, const void *k_pool,
+                                         const void *v_pool, long long pool_rows, const int *page_table, int table_width,
+                                         int ring_pages, int tokens_per_page, int max_positions, int *status,
+                                         void *stream) {
+    return ring_launch(q, q_row, out, n_rows, n_heads, n_kv_heads, head_dim, scale, window, token_seq, token_pos, seq_slot, k_pool,
+                       v_pool, pool_rows, page_table, table_width, ring_pages, tokens_per_page, max_positions, status, nullptr,
+                       stream);
+}
+
+// The same with q/k/v preparation taken in (src/model.c:247-259): the rows at q are as the q/k/v product left them
+// (q heads, then k heads, then v heads); q and k are normed with q_norm / k_norm [head_dim] (null: not) and eps, rotated
+// over the whole head in halves with cos / sin [positions, head_dim / 2] (null: not), and with keep != 0 the new
+// token's key and value are written to the pools. Rows, norms, angles and pools 16-byte aligned.
+extern "C" int abk_attention_decode_ring_prepare(const void *qkv, long long q_row, void *out, int n_rows, int n_heads,
+                                                 int n_kv_heads, int head_dim, float scale, int window,
+                                                 const int *token_seq, const int *token_pos, const int *seq_slot,
+                                                 void *k_pool, void *v_pool, long long pool_rows, const int *page_table,
+                                                 int table_width, int ring_pages, int tokens_per_page, int max_positions,
+                                                 const float *q_norm, const float *k_norm, float eps, const float *cos,
+                                                 const float *sin, int keep, int *status, void *stream) {
+    RingPrepare prepare = {q_norm, k_norm, cos, sin, eps, keep};
+    return ring_launch(qkv, q_row, out, n_rows, n_heads, n_kv_heads, head_dim, scale, window, token_seq, token_pos, seq_slot,
+                       k_pool, v_pool, pool_rows, page_table, table_width, ring_pages, tokens_per_page, max_positions, status,
+                       &prepare, stream);
 }

@@ -3,6 +3,7 @@
 // All arithmetic is float32; only what is stored may be bfloat16.
 #define ABK_DEFINE_ERROR
 #include "common.cuh"
+#include "qkv_prep.cuh"
 
 // ------------------------------------------------------------------ embedding
 // x[t, :] = float(table[tokens[t], :])                      (src/model.c:290-291)
@@ -291,50 +292,14 @@ template <typename T> __global__ void qkv_prep_kernel(QkvPrep p) {
 template <int HD>
 __device__ __forceinline__ void prep_head(const QkvPrep &p, uint4 raw_u, int head, bool live, int l, bool upper,
                                           const float *cs, const float *sn, __nv_bfloat16 *row0, long long kept_at) {
-    constexpr int LPH = HD / 8;
     const bool is_q = head < p.n_heads, is_k = !is_q && head < p.n_heads + p.n_kv_heads;
     const int kv_head = is_q ? 0 : is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
-    const uint32_t in[4] = {raw_u.x, raw_u.y, raw_u.z, raw_u.w};
-    float v[8];
-#pragma unroll
-    for (int e = 0; e < 4; e++) {
-        const float2 f = __bfloat1622float2(*(const __nv_bfloat162 *)&in[e]);
-        v[2 * e] = f.x, v[2 * e + 1] = f.y;
-    }
-    float ss = 0.0f;
-#pragma unroll
-    for (int e = 0; e < 8; e++) ss += v[e] * v[e];
-#pragma unroll
-    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);  // over the head's lanes
-    const float *w = is_q ? p.q_norm : p.k_norm;
-    if ((is_q || is_k) && w) {
-        const float scale = 1.0f / sqrtf(ss / (float)HD + p.eps);
-        const float4 w0 = __ldg((const float4 *)(w + l * 8)), w1 = __ldg((const float4 *)(w + l * 8 + 4));
-        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-        for (int e = 0; e < 8; e++) v[e] = wv[e] * (v[e] * scale);
-    }
-    // the element HD / 2 above or below each of this lane's, from the lane that holds it
-    float other[8];
-#pragma unroll
-    for (int e = 0; e < 8; e++) other[e] = __shfl_xor_sync(0xffffffffu, v[e], LPH / 2);
-    uint32_t outw[4] = {in[0], in[1], in[2], in[3]};
-    if (is_q || is_k) {
-        if (p.cos) {
-#pragma unroll
-            for (int e = 0; e < 8; e++) v[e] = upper ? v[e] * cs[e] + other[e] * sn[e] : v[e] * cs[e] - other[e] * sn[e];
-        }
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-            outw[e] = *(uint32_t *)&h2;
-        }
-        if (live) *(uint4 *)(row0 + (long long)head * HD) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
-    }
+    const uint4 done = prep_head_values<HD>(raw_u, is_q || is_k, is_q ? p.q_norm : p.k_norm, p.eps, p.cos != nullptr, l, upper, cs, sn);
+    if (live && (is_q || is_k)) *(uint4 *)(row0 + (long long)head * HD) = done;
     if (live && !is_q && kept_at >= 0) {
         __nv_bfloat16 *dst = (__nv_bfloat16 *)(is_k ? p.k_pool : p.v_pool) + kept_at +
                              (long long)kv_head * p.cache.tokens_per_page * HD + l * 8;
-        *(uint4 *)dst = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+        *(uint4 *)dst = done;
     }
 }
 

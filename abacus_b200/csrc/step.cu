@@ -46,6 +46,9 @@ typedef int (*AttnPrefillTcFn)(const void *, long long, int, void *, int, int, i
 typedef int (*AttnDecodeRingFn)(const void *, long long, void *, int, int, int, int, float, int, const int *, const int *,
                                 const int *, const void *, const void *, long long, const int *, int, int, int, int, int *,
                                 void *);
+typedef int (*AttnDecodeRingPrepareFn)(const void *, long long, void *, int, int, int, int, float, int, const int *, const int *,
+                                       const int *, void *, void *, long long, const int *, int, int, int, int, const float *,
+                                       const float *, float, const float *, const float *, int, int *, void *);
 typedef int (*AttnDecodeFn)(const void *, long long, void *, int, int, int, int, float, int, const int *, const int *,
                             const int *, const void *, const void *, const int *, int, int, int, int, float *, int *, int *,
                             void *);
@@ -65,6 +68,7 @@ struct AbkFns {
     AttnPrefillTcFn attention_prefill_tc;
     AttnDecodeRingFn attention_decode_ring;
     AttnDecodeFn attention_decode;
+    AttnDecodeRingPrepareFn attention_decode_ring_prepare;
 };
 
 // ------------------------------------------------------------------ the model, bound once
@@ -113,7 +117,8 @@ struct AbkModel {
     int *gemm_tickets, *kernel_status;
     float *halves;        // partial results of halved attention tiles
     int *halves_tickets, *attention_tickets;
-    int dtype, hidden, vocab, n_blocks, n_entries, halves_pairs, attention_ticket_count, pad;
+    int dtype, hidden, vocab, n_blocks, n_entries, halves_pairs, attention_ticket_count;
+    int decode_prepares;  // decode attention prepares q, k and v itself where it can (parts/attention.py: DECODE_PREPARES)
 };
 
 // ------------------------------------------------------------------ one step
@@ -194,7 +199,17 @@ static int attention(const AbkModel &m, const AbkAttention &a, const AbkEntry &e
     const bool writes = e.owns != 0, has_cache = e.k != nullptr;
     if (writes) TRY(linear(m, a.qkv, s.xn, m.hidden, s.qkv, m.dtype, row, n, stream), "the q/k/v product");
     else TRY(linear(m, a.q_only, s.xn, m.hidden, s.qkv, m.dtype, row, n, stream), "the q product");
-    TRY(LAUNCH(f.qkv_prep, s.qkv, m.dtype, n, a.n_heads, a.n_kv_heads, a.head_dim, writes ? 0 : 1, s.token_seq, s.token_pos,
+    const int group = a.n_heads / a.n_kv_heads, hd = a.head_dim;
+    const bool bf16 = m.dtype == ABK_BF16;
+    const size_t decode_smem = (size_t)4 * 64 * hd * 2 + (size_t)4 * group * (hd + 2) * 4 + 64;
+    const bool decode_takes = has_cache && (hd == 64 || hd == 128 || hd == 256) && e.tokens_per_page == 64 && decode_smem <= 200 * 1024;
+    // kernels/ops.py: attention_decode_prepares
+    const bool prepares = m.decode_prepares && s.is_decode && bf16 && decode_takes && hd != 256 && group <= 16 &&
+                          (!a.cos || (a.rotary_dim == hd && !a.interleaved)) && row % 8 == 0 && aligned16(s.qkv) &&
+                          aligned16(a.q_norm) && aligned16(a.k_norm) && aligned16(a.cos) && aligned16(a.sin) && aligned16(e.k) &&
+                          aligned16(e.v);
+    if (!prepares)
+        TRY(LAUNCH(f.qkv_prep, s.qkv, m.dtype, n, a.n_heads, a.n_kv_heads, a.head_dim, writes ? 0 : 1, s.token_seq, s.token_pos,
                    s.seq_slot, s.seq_len_after, a.q_norm, a.k_norm, a.eps, a.cos, a.sin, a.rotary_dim, a.interleaved,
                    writes ? e.k : nullptr, writes ? e.v : nullptr, writes ? e.table : nullptr, writes ? e.table_width : 0,
                    writes ? e.ring_pages : 0, writes ? e.tokens_per_page : 1, stream),
@@ -202,15 +217,16 @@ static int attention(const AbkModel &m, const AbkAttention &a, const AbkEntry &e
     // a windowed cache keeps only the last keys; a prompt reads its keys from this step's own rows
     const bool from_step = a.window > 0 && !s.is_decode;
     if (from_step && (s.any_continuation || !writes)) return fail(STEP_REFUSED_WINDOW, "windowed attention", entry);
-    const int group = a.n_heads / a.n_kv_heads, hd = a.head_dim;
-    const bool bf16 = m.dtype == ABK_BF16;
-    const size_t decode_smem = (size_t)4 * 64 * hd * 2 + (size_t)4 * group * (hd + 2) * 4 + 64;
-    const bool decode_takes = has_cache && (hd == 64 || hd == 128 || hd == 256) && e.tokens_per_page == 64 && decode_smem <= 200 * 1024;
     const bool prefill_takes = has_cache && (hd == 64 || hd == 128) && e.tokens_per_page == 64 && e.ring_pages == 0;
     const AbkLists *lists = a.lists >= 0 && a.lists < s.n_lists ? &s.lists[a.lists] : nullptr;
     if (s.is_decode && !from_step && bf16 && decode_takes) {
         const int bound = s.position_bound > 0 ? s.position_bound : s.max_len_after;
-        if (hd != 256 && group <= 16) {
+        if (prepares) {
+            TRY(LAUNCH(f.attention_decode_ring_prepare, s.qkv, row, s.att, n, a.n_heads, a.n_kv_heads, hd, a.scale, a.window,
+                       s.token_seq, s.token_pos, s.seq_slot, e.k, e.v, e.pool_rows, e.table, e.table_width, e.ring_pages,
+                       e.tokens_per_page, bound, a.q_norm, a.k_norm, a.eps, a.cos, a.sin, writes ? 1 : 0, m.kernel_status, stream),
+                "decode attention");
+        } else if (hd != 256 && group <= 16) {
             TRY(LAUNCH(f.attention_decode_ring, s.qkv, row, s.att, n, a.n_heads, a.n_kv_heads, hd, a.scale, a.window, s.token_seq,
                                         s.token_pos, s.seq_slot, e.k, e.v, e.pool_rows, e.table, e.table_width, e.ring_pages,
                                         e.tokens_per_page, bound, m.kernel_status, stream),

@@ -295,14 +295,18 @@ def sample_all(logits, temperature, rng_state, out, n_rows=None, rng_index=None)
                                    _p(rng_state), _p(rng_index), _p(out), _p(sums), _stream()), "sample_all", kernels=2)
 
 
-def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, ws=None, lists=None):
+def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, ws=None, lists=None,
+              prepare=None):
     """Attention of a step: picks the kernel for the phase and sizes; every case the faster kernels
     do not take goes to the general one. lists: the step's tiles and work list for the prefill kernels
-    (parts/attention_plan.py: AttentionLists); without them a step of several tokens runs on the general kernel."""
+    (parts/attention_plan.py: AttentionLists); without them a step of several tokens runs on the general kernel.
+    prepare: see attention_decode (only where attention_decode_prepares() said yes for this step)."""
     if (batch.is_decode and not from_step and ws is not None and qkv.dtype == torch.bfloat16
             and attention_decode_takes(n_heads, n_kv_heads, head_dim, cache)):
-        attention_decode(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws)
-    elif (not batch.is_decode and not from_step and not window and qkv.dtype == torch.bfloat16 and lists is not None
+        attention_decode(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, prepare=prepare)
+        return
+    assert prepare is None, "q, k and v must be prepared before any kernel but decode attention's"
+    if (not batch.is_decode and not from_step and not window and qkv.dtype == torch.bfloat16 and lists is not None
           and attention_prefill_takes(head_dim, cache)):
         attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cache, lists)
     else:
@@ -349,7 +353,20 @@ def attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cac
         _i(cache.tokens_per_page), _p(kernel_status(qkv.device)), _stream()), "attention_prefill")
 
 
-def _attention_decode_mma(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, max_positions):
+def attention_decode_prepares(qkv, n_heads, n_kv_heads, head_dim, cache, q_norm, k_norm, cos, sin, rotary_dim, interleaved):
+    """Whether decode attention takes the q/k/v preparation (per-head norm, rotation, the new token's key and value
+    into the cache) into its own kernel: on the tensor-core kernel, with the rotation over the whole head in halves
+    (or none), and everything 16-byte aligned."""
+    tensors = [t for t in (qkv, q_norm, k_norm, cos, sin, cache.k, cache.v) if t is not None]
+    return (qkv.dtype == torch.bfloat16 and head_dim in (64, 128) and n_heads // n_kv_heads <= 16
+            and attention_decode_takes(n_heads, n_kv_heads, head_dim, cache)
+            and (cos is None or (rotary_dim == head_dim and not interleaved))
+            and all(t.data_ptr() % 16 == 0 for t in tensors) and qkv.stride(0) % 8 == 0
+            and all(t is None or t.dtype == torch.float32 for t in (q_norm, k_norm, cos, sin)))
+
+
+def _attention_decode_mma(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, max_positions,
+                          prepare=None):
     lib = load_module("attention_decode_ring")
     n = batch.n_rows
     row = (n_heads + 2 * n_kv_heads) * head_dim
@@ -359,6 +376,18 @@ def _attention_decode_mma(qkv, out, n_heads, n_kv_heads, head_dim, scale, window
     if batch.max_len_after > max_positions:
         raise KernelError(f"a row at position {batch.max_len_after - 1} is beyond the bound {max_positions}")
     pool_rows = cache.k.shape[0] * cache.k.shape[1] * cache.k.shape[2]
+    if prepare is not None:
+        cos = prepare["cos"]
+        if cos is not None and batch.max_position >= cos.shape[0]:
+            raise KernelError(f"position {batch.max_position} is beyond the rotary table of {cos.shape[0]} positions")
+        _check(lib, lib.abk_attention_decode_ring_prepare(
+            _p(qkv), _ll(row), _p(out), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _i(window or 0),
+            _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(cache.k), _p(cache.v), _ll(pool_rows),
+            _p(cache.page_table), _i(cache.table_width), _i(cache.ring_pages), _i(cache.tokens_per_page),
+            _i(max_positions), _p(prepare["q_norm"]), _p(prepare["k_norm"]), _f(prepare["eps"] or 0.0), _p(cos),
+            _p(prepare["sin"]), _i(1 if prepare["keep"] else 0), _p(kernel_status(qkv.device)), _stream()),
+            "attention_decode_mma")
+        return
     _check(lib, lib.abk_attention_decode_ring(
         _p(qkv), _ll(row), _p(out), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale), _i(window or 0),
         _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(cache.k), _p(cache.v), _ll(pool_rows),
@@ -373,18 +402,22 @@ def attention_decode_takes(n_heads, n_kv_heads, head_dim, cache):
 
 
 def attention_decode(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, max_positions=None,
-                     simt=False):
+                     simt=False, prepare=None):
     """One new token per row against the paged bfloat16 cache, split along the keys (src/model.c:197-211).
 
     Head sizes 64 and 128 with groups of up to 16 query heads run on the tensor cores (mma.sync);
     head size 256, larger groups, or simt=True, on the CUDA cores.
     max_positions bounds every row's position + 1 (it sizes the grid and the scratch); by default
     the step's own maximum. A captured graph passes the bound it was captured for.
+    prepare: dict(q_norm, k_norm, eps, cos, sin, keep) where attention_decode_prepares() says so: qkv is as the
+    product left it, and the kernel norms and rotates q and k and (keep) writes the new key and value to the cache
+    itself (src/model.c:247-259).
     """
     _need_cuda(qkv, out)
     if not simt and head_dim in (64, 128) and n_heads // n_kv_heads <= 16:
         return _attention_decode_mma(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws,
-                                     max_positions)
+                                     max_positions, prepare)
+    assert prepare is None, "only the tensor-core kernel prepares q, k and v itself"
     lib = load_module("attention_decode")
     lib.abk_attention_decode_scratch_floats.restype = ctypes.c_longlong
     n = batch.n_rows

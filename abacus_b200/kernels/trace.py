@@ -30,6 +30,8 @@ def read(max_records=16384, lives=False):
         raise RuntimeError("the kernel libraries are built without records: set ABACUS_TRACE=1 before importing")
     out = []
     for module, lib in list(build._loaded.items()):
+        if not hasattr(lib, "abk_trace_read"):  # a library without device code keeps no records
+            continue
         buf = (Record * max_records)()
         n = lib.abk_trace_read(buf, ctypes.c_int(max_records))
         if n < 0:

@@ -4,6 +4,8 @@ The mixer owns the q/k/v and output projections, the optional per-head norm of
 q and k, and a position encoding; its sizes, scale, eps and window come from
 its spec. q, k and v are one stacked matrix, as in src/model.c:88-93.
 """
+import os
+
 import torch
 
 from ..cache.need import CacheNeed
@@ -11,6 +13,11 @@ from ..kernels import ops
 from .attention_plan import AttentionLists, AttentionStepPlan
 from .base import MIXERS, POSITIONS, to_device
 from .linear import Linear
+
+
+# A decode step's attention kernel can norm and rotate q and k and write the new key and value to the cache itself: a
+# launch less in every layer. ABACUS_DECODE_PREPARES=0 keeps the preparation a kernel of its own (for comparison).
+DECODE_PREPARES = os.environ.get("ABACUS_DECODE_PREPARES", "1") != "0"
 
 
 @MIXERS.register("attention")
@@ -74,10 +81,16 @@ class Attention:
             self.qkv_proj.forward(xn, qkv, n)
         else:  # keys and values are another entry's: only q is needed
             self.q_proj.forward(xn, qkv[:, :self.q_size], n)
-        ops.qkv_prep(qkv, s.n_heads, s.n_kv_heads, s.head_dim, batch, self.q_norm, self.k_norm, s.qk_norm_eps,
-                     self.cos, self.sin, self.position.rotary_dim if self.position else 0,
-                     self.position.interleaved if self.position else False, cache.kv if writes else None,
-                     q_only=not writes)
+        rotary_dim = self.position.rotary_dim if self.position else 0
+        interleaved = self.position.interleaved if self.position else False
+        prepare = None
+        if (DECODE_PREPARES and batch.is_decode and cache.kv is not None
+                and ops.attention_decode_prepares(qkv, s.n_heads, s.n_kv_heads, s.head_dim, cache.kv, self.q_norm,
+                                                  self.k_norm, self.cos, self.sin, rotary_dim, interleaved)):
+            prepare = dict(q_norm=self.q_norm, k_norm=self.k_norm, eps=s.qk_norm_eps, cos=self.cos, sin=self.sin, keep=writes)
+        else:
+            ops.qkv_prep(qkv, s.n_heads, s.n_kv_heads, s.head_dim, batch, self.q_norm, self.k_norm, s.qk_norm_eps,
+                         self.cos, self.sin, rotary_dim, interleaved, cache.kv if writes else None, q_only=not writes)
         # A windowed cache keeps only the last keys; a prompt longer than that reads its keys from
         # this step's own rows, which hold all of them when the sequences start at position 0.
         from_step = s.window is not None and not batch.is_decode
@@ -86,6 +99,6 @@ class Attention:
                                     "and only with keys of its own")
         mine = batch.plan.get(self.lists.name)
         ops.attention(qkv, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, batch, cache.kv,
-                      from_step=from_step, ws=ws, lists=AttentionLists(mine) if mine is not None else None)
+                      from_step=from_step, ws=ws, lists=AttentionLists(mine) if mine is not None else None, prepare=prepare)
         self.o_proj.forward(att, out, n)
         return out

@@ -263,10 +263,11 @@ class Harness:
         self.cache = SequenceCache([CacheNeed(hkv, hd, window)], [None], max_tokens, dtype, "cuda", max_context=1024)
 
     def step(self, ops, seqs, qkv, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved, scale, from_step=False,
-             general=True, simt=False):
+             general=True, simt=False, prepares=False):
         """seqs: [(slot, n_new)]; qkv float32 numpy [rows, (hq + 2 hkv) * hd]. Returns attention output.
         general=False lets ops.attention pick the kernel for the phase, as the model does; simt=True sends a decode
-        step to the CUDA-core decode kernel whatever the head size."""
+        step to the CUDA-core decode kernel whatever the head size; prepares=True leaves the preparation of q, k and v
+        to the decode attention kernel."""
         from abacus_b200.engine.batch import Sequence, StepBatch
         ss = []
         for slot, n in seqs:
@@ -280,7 +281,12 @@ class Harness:
         pad = np.full((3, qkv.shape[1]), 7.0, dtype=np.float32)
         q = dev(np.concatenate([qkv, pad]), self.dtype)
         kv = self.cache.views[0].kv
-        ops.qkv_prep(q, self.hq, self.hkv, self.hd, batch, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved, kv)
+        prepare = None
+        if prepares:
+            assert ops.attention_decode_prepares(q, self.hq, self.hkv, self.hd, kv, q_norm, k_norm, cos, sin, rotary_dim, interleaved)
+            prepare = dict(q_norm=q_norm, k_norm=k_norm, eps=eps, cos=cos, sin=sin, keep=True)
+        else:
+            ops.qkv_prep(q, self.hq, self.hkv, self.hd, batch, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved, kv)
         out = torch.full((rows + 3, self.hq * self.hd), 5.0, dtype=self.dtype, device="cuda")
         if general:
             ops.attention_generic(q, out, self.hq, self.hkv, self.hd, scale, self.window, batch, kv, from_step=from_step)
@@ -292,7 +298,7 @@ class Harness:
             from abacus_b200.parts import Workspace
             self.ws = getattr(self, "ws", None) or Workspace(torch.device("cuda", 0))
             ops.attention(q, out, self.hq, self.hkv, self.hd, scale, self.window, batch, kv, from_step=from_step,
-                          ws=self.ws, lists=lists)
+                          ws=self.ws, lists=lists, prepare=prepare)
         for slot, n in seqs:
             self.cache.advance(slot, n)
         if general or all(n == 1 for _, n in seqs):
@@ -571,6 +577,46 @@ def test_decode_attention_split_along_the_keys(ops, hq, hkv, hd, window, simt):
         v = d[:, (hq + hkv) * hd:].reshape(n, hkv, hd)
         want = plain.attention(q, k, v, window, rnd=bf)[-1].reshape(hq * hd)
         np.testing.assert_allclose(got[i], want, rtol=2 ** -7, atol=2 ** -7, err_msg=f"row {i} of length {n}")
+    assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
+
+
+@pytest.mark.parametrize("hq, hkv, hd, window, norm, rotated", [
+    (16, 8, 128, None, True, True), (6, 2, 64, None, True, True), (32, 8, 128, None, True, True), (4, 4, 128, None, False, True),
+    (3, 1, 64, None, True, False), (8, 1, 64, 129, False, False), (4, 2, 128, 200, True, True), (16, 1, 128, 64, True, True)])
+def test_decode_attention_prepares_its_heads(ops, hq, hkv, hd, window, norm, rotated):
+    """Decode attention that norms and rotates q and k and writes the new key and value to the cache itself, against
+    the preparation's own kernel followed by attention: the same bits in the output and in the cache, over three decode
+    steps in a row (the later ones read what the earlier ones wrote). The rows' lengths put the new token into every
+    quarter of a page, at a page's first and last place, and into a sequence's very first place."""
+    rng = np.random.default_rng(hq * 100 + hd + (window or 0))
+    lens = [1, 2, 16, 17, 33, 50, 64, 65, 127, 128, 129, 257, 700, 383]
+    width = (hq + 2 * hkv) * hd
+    scale = 1.0 / np.sqrt(hd)
+    qn = dev(1.0 + 0.3 * rng.standard_normal(hd), torch.float32) if norm else None
+    kn = dev(1.0 + 0.3 * rng.standard_normal(hd), torch.float32) if norm else None
+    angles = rng.uniform(0, 6.28, (1024, hd // 2))
+    cos = dev(np.cos(angles), torch.float32) if rotated else None
+    sin = dev(np.sin(angles), torch.float32) if rotated else None
+    prep = (qn, kn, 1e-5, cos, sin, hd if rotated else 0, False, scale)
+    data = [bf(rng.standard_normal((n + 2, width)) * 1.5) for n in lens]
+    results = []
+    for prepares in (False, True):
+        h = Harness(hq, hkv, hd, torch.bfloat16, window, max_tokens=64 * 60)
+        slots = [h.cache.open_slot() for _ in lens]
+        for slot, d, n in zip(slots, data, lens):
+            if n > 1:
+                h.step(ops, [(slot, n - 1)], d[:n - 1], *prep, from_step=window is not None)
+        outs = []
+        for t in range(3):
+            rows = np.concatenate([d[n - 1 + t:n + t] for d, n in zip(data, lens)])
+            outs.append(h.step(ops, [(slot, 1) for slot in slots], rows, *prep, general=False, prepares=prepares)[1])
+        kv = h.cache.views[0].kv
+        results.append((np.stack(outs), kv.k.clone(), kv.v.clone(), kv.page_table.clone()))
+    (out_a, k_a, v_a, table_a), (out_b, k_b, v_b, table_b) = results
+    assert torch.equal(table_a, table_b)
+    assert np.array_equal(out_a, out_b)
+    assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
+    assert np.isfinite(out_a).all() and np.abs(out_a).max() > 0.1
     assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
 
 
