@@ -33,6 +33,8 @@
 #include <mutex>
 #include <unordered_map>
 
+#include "qkv_prep.cuh"
+
 #define TILE_P 128
 #define TILE_K 64
 #define GEMM_THREADS 192
@@ -55,6 +57,10 @@ template <int BN, int STAGES> struct GemmSmem {
     static constexpr int BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /* alignment */ + 256 /* barriers */;
 };
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *(uint32_t *)&t;
+}
 // 16 consecutive results of one row, stored as 16-byte vectors.
 __device__ __forceinline__ void store16(float *dst, const uint32_t *v) {
 #pragma unroll
@@ -264,6 +270,138 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
     }
 }
 
+// ------------------------------------------------------------------ what may follow a product in its kernel
+#define EPI_PLAIN 0
+#define EPI_GATED 1  // silu(gate) * up of a tile that holds both (see the persistent kernel)
+#define EPI_QKV 2    // the q/k/v product of a prompt with the step between it and attention taken in
+// EPI_QKV (column tiles of 256 = two heads of 128, bfloat16 out): the rows are tokens, the columns q heads, then k
+// heads, then v heads, and a thread that stores a row holds whole heads of it. It does what the preparation kernel
+// does to them (src/model.c:247-259; qkv_prep.cuh, to the same bits): q and k normed over the head and rotated, q
+// stored to out, k and v of a token that belongs to a sequence to their place in the paged cache and nowhere else.
+struct QkvEpilogue {
+    const int *token_seq, *token_pos, *seq_slot;
+    const float *q_norm, *k_norm;  // [128]; null: no norm
+    const float *cos, *sin;        // [positions, 64]; null: no rotation
+    float eps;
+    __nv_bfloat16 *k_pool, *v_pool;
+    PagedCache cache;
+    int n_heads, n_kv_heads;
+};
+// A kernel with this epilogue has eight storing warps, two to each quarter of the tile's rows (a warp reaches only its
+// quarter of the lanes of tensor memory): warp `part` of a quarter takes the pairs (i, i + 64) of a head with i in
+// [32 part, 32 part + 32), that is 64 of a row's 128 values, and reads all 128 only to add up their squares. A single warp
+// to a scheduler cannot hide the latency of its own instructions; two, each with half of the work, take a third of the time.
+// A row's angles (64 cos, 64 sin) lie 256 bytes from the next row's. A warp asks for its 32 of each for its 32 rows as soon
+// as it knows the tile, before it waits for the accumulator: asynchronous copies that cover whole lines, into its own
+// QKV_ANGLE_FLOATS floats of shared memory (cos of the 32 rows, then sin), from where every thread later reads its row's.
+#define QKV_THREADS 320  // one warp that loads, one that multiplies, eight that store
+#define QKV_ANGLE_FLOATS (2 * 32 * 32)
+// Where the four angles from `c` on (a multiple of 4 below 32) of row `row` lie among a table's 32 rows of 32: the 16-byte
+// pieces of a row are exchanged by the row's last three bits, so that reads of the same piece of 8 rows fall into different banks.
+__device__ __forceinline__ int qkv_angle_at(int row, int c) { return row * 32 + ((((c >> 2) ^ (row & 7)) << 2)); }
+// What a thread knows of its row before the accumulator is there: the token's sequence (-1: none) and position, and where its
+// keys and values go in the pools (kv head 0; -1: nowhere). Looked up, like the angles, while the tile is still being multiplied.
+struct QkvRow {
+    int seq, pos;
+    long long kept_at;
+};
+__device__ __forceinline__ QkvRow fetch_qkv_angles(int p, int part, const GemmTc &g, const QkvEpilogue &e, float *angles) {
+    const int lane = threadIdx.x & 31;
+    QkvRow r;
+    r.seq = p < g.P ? e.token_seq[p] : -1;
+    r.pos = p < g.P ? e.token_pos[p] : 0;  // (asked for with the sequence, not after it)
+    if (r.seq < 0) r.pos = 0;
+    r.kept_at = -1;
+    if (r.seq >= 0 && e.k_pool) r.kept_at = cache_offset(e.cache, cache_page(e.cache, e.seq_slot[r.seq], r.pos), 0, e.n_kv_heads, r.pos, 128);
+    if (!e.cos) return r;
+    const int pos = r.pos;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {  // lane l copies the 16-byte piece l % 8 of row l / 8 + 4 j
+        const int row = (lane >> 3) + 4 * j, c = 4 * (lane & 7);
+        const long long at = (long long)__shfl_sync(0xffffffffu, pos, row) * 64 + 32 * part + c;
+        const uint32_t to_cos = tc::smem_addr(angles + qkv_angle_at(row, c)), to_sin = tc::smem_addr(angles + 32 * 32 + qkv_angle_at(row, c));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to_cos), "l"(e.cos + at) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to_sin), "l"(e.sin + at) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    return r;
+}
+// One row p of a tile whose first column is q0: the accumulator's 256 columns start at tensor-memory address `acc` (this
+// warp's lanes). Whole warps call it, after fetch_qkv_angles() for the same rows and part.
+template <int PART>
+__device__ __forceinline__ void store_qkv_row(uint32_t acc, int p, int q0, const GemmTc &g, const QkvEpilogue &e, const float *angles,
+                                              const QkvRow &r) {
+    const int lane = threadIdx.x & 31;
+    if (e.cos) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+    }
+#pragma unroll 1
+    for (int h = 0; h < 2; h++) {
+        const int head = q0 / 128 + h;
+        if (head * 128 >= g.Q) break;
+        float mine[64], part[16];  // elements 32 PART .. + 31 and 64 + 32 PART .. + 31 of the head; every eight's sum of squares
+#pragma unroll
+        for (int c = 0; c < 4; c++) {  // 32 columns at a time
+            float t[32];
+            tc::tmem_ld16(acc + h * 128 + 32 * c, (uint32_t *)t);
+            tc::tmem_ld16(acc + h * 128 + 32 * c + 16, (uint32_t *)t + 16);
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i++) t[i] = prep_through_bf16(t[i]);
+#pragma unroll
+            for (int l = 0; l < 4; l++) part[4 * c + l] = prep_sumsq8(t + 8 * l);
+            if (c == PART || c == 2 + PART) {
+#pragma unroll
+                for (int i = 0; i < 32; i++) mine[(c == PART ? 0 : 32) + i] = t[i];
+            }
+        }
+        const bool is_q = head < e.n_heads, is_k = !is_q && head < e.n_heads + e.n_kv_heads;
+        const float *w = is_q ? e.q_norm : e.k_norm;
+        if ((is_q || is_k) && w) {
+            const float scale = prep_scale<128>(prep_fold<128>(part), e.eps);
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                const float4 lo = __ldg((const float4 *)(w + 32 * PART + i)), hi = __ldg((const float4 *)(w + 64 + 32 * PART + i));
+                mine[i] = prep_normed(lo.x, mine[i], scale), mine[i + 1] = prep_normed(lo.y, mine[i + 1], scale);
+                mine[i + 2] = prep_normed(lo.z, mine[i + 2], scale), mine[i + 3] = prep_normed(lo.w, mine[i + 3], scale);
+                mine[32 + i] = prep_normed(hi.x, mine[32 + i], scale), mine[33 + i] = prep_normed(hi.y, mine[33 + i], scale);
+                mine[34 + i] = prep_normed(hi.z, mine[34 + i], scale), mine[35 + i] = prep_normed(hi.w, mine[35 + i], scale);
+            }
+        }
+        if ((is_q || is_k) && e.cos) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                const float4 c4 = *(const float4 *)(angles + qkv_angle_at(lane, i)), s4 = *(const float4 *)(angles + 32 * 32 + qkv_angle_at(lane, i));
+                const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const float lo = mine[i + k], hi = mine[32 + i + k];
+                    mine[i + k] = prep_rotated_lower(lo, hi, cs[k], sn[k]);
+                    mine[32 + i + k] = prep_rotated_upper(hi, lo, cs[k], sn[k]);
+                }
+            }
+        }
+        __nv_bfloat16 *dst = nullptr;
+        if (is_q) {
+            if (p < g.P) dst = (__nv_bfloat16 *)g.out + (long long)p * g.stride_p + head * 128;
+        } else if (r.kept_at >= 0) {
+            const int kv_head = is_k ? head - e.n_heads : head - e.n_heads - e.n_kv_heads;
+            dst = (is_k ? e.k_pool : e.v_pool) + r.kept_at + (long long)kv_head * e.cache.tokens_per_page * 128;
+        }
+        if (dst) {
+#pragma unroll
+            for (int half = 0; half < 2; half++)
+#pragma unroll
+                for (int i = 0; i < 32; i += 8)
+                    *(uint4 *)(dst + 64 * half + 32 * PART + i) =
+                        make_uint4(pack2(mine[32 * half + i], mine[32 * half + i + 1]), pack2(mine[32 * half + i + 2], mine[32 * half + i + 3]),
+                                   pack2(mine[32 * half + i + 4], mine[32 * half + i + 5]), pack2(mine[32 * half + i + 6], mine[32 * half + i + 7]));
+        }
+    }
+    __syncwarp();  // every lane has read its angles before the next tile's are asked for
+}
+
 // ------------------------------------------------------------------ persistent kernel for many tiles
 // Tile t is rows (t % m_tiles) * 128 and columns (t / m_tiles) * BN; CTA c takes tiles c, c + grid, ...
 // Warp 0 loads, warp 1 issues the products into accumulator (i & 1) of its i-th tile, warps 2-5 store
@@ -273,10 +411,11 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
 // rounded to bfloat16 first, as they are where they are stored between the product and the activation: the
 // feed-forward's first product and its activation in one (src/model.c:274-282, 307-308). g.Q is then the
 // number of features, half of the product's columns.
-template <int BN, int STAGES, typename TO, bool GATED = false>
-__global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p,
+template <int BN, int STAGES, typename TO, int EPI = EPI_PLAIN>
+__global__ void __launch_bounds__(EPI == EPI_QKV ? QKV_THREADS : GEMM_THREADS) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p,
                                                                           const __grid_constant__ CUtensorMap map_q,
-                                                                          GemmTc g, int m_tiles, int tiles) {
+                                                                          GemmTc g, int m_tiles, int tiles, QkvEpilogue qkv) {
+    constexpr bool GATED = EPI == EPI_GATED;
     using S = GemmSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -285,12 +424,13 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_persistent_kernel(const 
     uint64_t *empty = full + STAGES, *acc_full = empty + STAGES, *acc_empty = acc_full + 2;
     uint32_t *tmem_holder = (uint32_t *)(acc_empty + 2);
     volatile int *flags = (volatile int *)(tmem_holder + 1);  // [0]: a wait ran out
+    float *qkv_angles = (float *)(smem + STAGES * (S::A_BYTES + S::B_BYTES) + 256);  // (EPI_QKV: see store_qkv_row)
     constexpr uint32_t TMEM_COLS = 2 * BN;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) tc::mbar_init(&full[s], 1), tc::mbar_init(&empty[s], 1);
-        for (int b = 0; b < 2; b++) tc::mbar_init(&acc_full[b], 1), tc::mbar_init(&acc_empty[b], 4);
+        for (int b = 0; b < 2; b++) tc::mbar_init(&acc_full[b], 1), tc::mbar_init(&acc_empty[b], EPI == EPI_QKV ? 8 : 4)  /* every storing warp */;
         flags[0] = 0;
         tc::mbar_init_fence();
         tc::tma_prefetch_map(&map_p), tc::tma_prefetch_map(&map_q);
@@ -368,6 +508,8 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_persistent_kernel(const 
         for (int t = blockIdx.x; t < tiles; t += gridDim.x, it++) {
             const int b = it & 1;
             const int p = (t % m_tiles) * TILE_P + row, q0 = (t / m_tiles) * BN;
+            QkvRow qkv_row = {-1, 0, -1};
+            if constexpr (EPI == EPI_QKV) qkv_row = fetch_qkv_angles(p, (warp - 2) >> 2, g, qkv, qkv_angles + (warp - 2) * QKV_ANGLE_FLOATS);
             // every lane takes the same way out: the loads from tensor memory below are for whole warps
             const bool ok = __all_sync(0xffffffffu, !flags[0] && tc::mbar_wait(&acc_full[b], (it >> 1) & 1));
             if (!ok) {
@@ -396,6 +538,9 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_persistent_kernel(const 
                         store16(out + (long long)p * g.stride_p + f0 + c0 + 16, gv + 16);
                     }
                 }
+            } else if constexpr (EPI == EPI_QKV) {
+                if ((warp - 2) >> 2) store_qkv_row<1>(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN, p, q0, g, qkv, qkv_angles + (warp - 2) * QKV_ANGLE_FLOATS, qkv_row);
+                else store_qkv_row<0>(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN, p, q0, g, qkv, qkv_angles + (warp - 2) * QKV_ANGLE_FLOATS, qkv_row);
             } else {
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -455,10 +600,11 @@ template <int BN, int STAGES> struct PairSmem {
     static constexpr int BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /* alignment */ + 256 /* barriers */;
 };
 
-template <int BN, int STAGES, typename TO, bool GATED = false>
-__global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p,
+template <int BN, int STAGES, typename TO, int EPI = EPI_PLAIN>
+__global__ void __launch_bounds__(EPI == EPI_QKV ? QKV_THREADS : GEMM_THREADS) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p,
                                                                     const __grid_constant__ CUtensorMap map_q, GemmTc g,
-                                                                    int m_tiles, int tiles) {
+                                                                    int m_tiles, int tiles, QkvEpilogue qkv) {
+    constexpr bool GATED = EPI == EPI_GATED;
     using S = PairSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -467,6 +613,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_pair_kernel(const __grid
     uint64_t *empty = full + STAGES, *acc_full = empty + STAGES, *acc_empty = acc_full + 2;
     uint32_t *tmem_holder = (uint32_t *)(acc_empty + 2);
     volatile int *flags = (volatile int *)(tmem_holder + 1);  // [0]: a wait ran out
+    float *qkv_angles = (float *)(smem + STAGES * (S::A_BYTES + S::B_BYTES) + 256);  // (EPI_QKV: see store_qkv_row)
     constexpr uint32_t TMEM_COLS = 2 * BN;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -474,7 +621,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_pair_kernel(const __grid
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) tc::mbar_init(&full[s], 1), tc::mbar_init(&empty[s], 1);
-        for (int b = 0; b < 2; b++) tc::mbar_init(&acc_full[b], 1), tc::mbar_init(&acc_empty[b], 8);  // four warps of each CTA
+        for (int b = 0; b < 2; b++) tc::mbar_init(&acc_full[b], 1), tc::mbar_init(&acc_empty[b], EPI == EPI_QKV ? 16 : 8);  // every storing warp of both CTAs
         flags[0] = 0;
         tc::mbar_init_fence();
         tc::tma_prefetch_map(&map_p), tc::tma_prefetch_map(&map_q);
@@ -552,6 +699,8 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_pair_kernel(const __grid
         for (int t = pair; t < tiles; t += pairs, it++) {
             const int b = it & 1;
             const int p = (t % m_tiles) * (2 * TILE_P) + rank * TILE_P + row, q0 = (t / m_tiles) * BN;
+            QkvRow qkv_row = {-1, 0, -1};
+            if constexpr (EPI == EPI_QKV) qkv_row = fetch_qkv_angles(p, (warp - 2) >> 2, g, qkv, qkv_angles + (warp - 2) * QKV_ANGLE_FLOATS);
             const bool ok = __all_sync(0xffffffffu, !flags[0] && tc::mbar_wait(&acc_full[b], (it >> 1) & 1));
             if (!ok) {
                 flags[0] = 1;
@@ -579,6 +728,9 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_pair_kernel(const __grid
                         store16(out + (long long)p * g.stride_p + f0 + c0 + 16, gv + 16);
                     }
                 }
+            } else if constexpr (EPI == EPI_QKV) {
+                if ((warp - 2) >> 2) store_qkv_row<1>(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN, p, q0, g, qkv, qkv_angles + (warp - 2) * QKV_ANGLE_FLOATS, qkv_row);
+                else store_qkv_row<0>(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN, p, q0, g, qkv, qkv_angles + (warp - 2) * QKV_ANGLE_FLOATS, qkv_row);
             } else {
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -692,14 +844,16 @@ static int launch(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g,
 }
 
 // The kernel for pairs of CTAs: m_tiles and tiles count tiles of 256 rows; one cluster of two CTAs per pair of SMs.
-template <int BN, int STAGES, typename TO, bool GATED = false>
-static int launch_pair(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g, int m_tiles, int tiles, cudaStream_t s) {
-    auto kernel = gemm_tc_pair_kernel<BN, STAGES, TO, GATED>;
-    constexpr int bytes = PairSmem<BN, STAGES>::BYTES;
+template <int BN, int STAGES, typename TO, int EPI = EPI_PLAIN>
+static int launch_pair(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g, int m_tiles, int tiles, cudaStream_t s,
+                       const QkvEpilogue &qkv = QkvEpilogue()) {
+    auto kernel = gemm_tc_pair_kernel<BN, STAGES, TO, EPI>;
+    constexpr int bytes = PairSmem<BN, STAGES>::BYTES + (EPI == EPI_QKV ? 8 * QKV_ANGLE_FLOATS * 4 : 0);
+    constexpr int threads = EPI == EPI_QKV ? QKV_THREADS : GEMM_THREADS;
     if (cudaError_t e = abk_allow_shared_memory((const void *)kernel, bytes)) return (int)e;  // once per device
     const int pairs = abk_sm_count() / 2;
-    abk_launch_clusters(kernel, dim3(2 * (tiles < pairs ? tiles : pairs)), dim3(GEMM_THREADS), (size_t)bytes, s, 2, mp, mq, g,
-                        m_tiles, tiles);
+    abk_launch_clusters(kernel, dim3(2 * (tiles < pairs ? tiles : pairs)), dim3(threads), (size_t)bytes, s, 2, mp, mq, g,
+                        m_tiles, tiles, qkv);
     return ABK_LAUNCH_RESULT();
 }
 // Whether a product of many rows goes to the pairs: enough tiles of 256 x 256 to give most pairs of SMs one.
@@ -708,13 +862,15 @@ static bool pairs_win(int M, int N) {
     return M > 256 && N >= 256 && tiles >= (abk_sm_count() / 2) * 6 / 7;
 }
 
-template <int BN, int STAGES, typename TO>
+template <int BN, int STAGES, typename TO, int EPI = EPI_PLAIN>
 static int launch_persistent(const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g, int m_tiles, int tiles,
-                             cudaStream_t s) {
-    auto kernel = gemm_tc_persistent_kernel<BN, STAGES, TO>;
-    constexpr int bytes = GemmSmem<BN, STAGES>::BYTES;
+                             cudaStream_t s, const QkvEpilogue &qkv = QkvEpilogue()) {
+    auto kernel = gemm_tc_persistent_kernel<BN, STAGES, TO, EPI>;
+    constexpr int bytes = GemmSmem<BN, STAGES>::BYTES + (EPI == EPI_QKV ? 8 * QKV_ANGLE_FLOATS * 4 : 0);
+    constexpr int threads = EPI == EPI_QKV ? QKV_THREADS : GEMM_THREADS;
     if (cudaError_t e = abk_allow_shared_memory((const void *)kernel, bytes)) return (int)e;  // once per device
-    abk_launch(kernel, dim3(tiles < abk_sm_count() ? tiles : abk_sm_count()), dim3(GEMM_THREADS), (size_t)bytes, s, mp, mq, g, m_tiles, tiles);
+    abk_launch(kernel, dim3(tiles < abk_sm_count() ? tiles : abk_sm_count()), dim3(threads), (size_t)bytes, s, mp, mq, g, m_tiles, tiles,
+               qkv);
     return ABK_LAUNCH_RESULT();
 }
 
@@ -739,15 +895,52 @@ extern "C" int abk_gemm_tc_swiglu(const void *x, const void *w, void *act, int M
         rc = tensor_map(w, 2LL * N, K, ldw, 128, &mw_half);
         if (rc) return rc;
         const int m_tiles2 = (M + 2 * TILE_P - 1) / (2 * TILE_P);
-        return launch_pair<256, 6, __nv_bfloat16, true>(mx, mw_half, g, m_tiles2, m_tiles2 * (N / 128), (cudaStream_t)stream);
+        return launch_pair<256, 6, __nv_bfloat16, EPI_GATED>(mx, mw_half, g, m_tiles2, m_tiles2 * (N / 128), (cudaStream_t)stream);
     }
     const int m_tiles = (M + TILE_P - 1) / TILE_P, tiles = m_tiles * (N / 128);
-    auto kernel = gemm_tc_persistent_kernel<256, 4, __nv_bfloat16, true>;
-    constexpr int bytes = GemmSmem<256, 4>::BYTES;
-    if (cudaError_t e = abk_allow_shared_memory((const void *)kernel, bytes)) return (int)e;  // once per device
-    abk_launch(kernel, dim3(tiles < abk_sm_count() ? tiles : abk_sm_count()), dim3(GEMM_THREADS), (size_t)bytes, (cudaStream_t)stream, mx, mw, g,
-               m_tiles, tiles);
-    return ABK_LAUNCH_RESULT();
+    return launch_persistent<256, 4, __nv_bfloat16, EPI_GATED>(mx, mw, g, m_tiles, tiles, (cudaStream_t)stream);
+}
+
+// qkv[M, :n_heads * 128] = the prepared q heads of x . w^T, and the prepared k and the v heads of every token that
+// belongs to a sequence into the paged cache (src/model.c:299 with 247-259): the q/k/v product of a prompt with what
+// stands between it and attention in its epilogue. w [(n_heads + 2 n_kv_heads) * 128, K] holds q heads, then k heads,
+// then v heads, of 128 each; the k and v columns of qkv are not written. q_norm / k_norm [128] float32 or null; cos / sin
+// [positions, 64] float32 or null (the rotation over the whole head in halves); pools [pages, n_kv_heads,
+// tokens_per_page, 128] bfloat16, the cache's own, all kept. Many rows only (more than 256); other shapes are refused
+// (the caller multiplies and prepares in two steps).
+extern "C" int abk_gemm_tc_qkv(const void *x, const void *w, void *qkv, int M, int n_heads, int n_kv_heads, int K, long long ldx,
+                               long long ldw, long long ldo, const int *token_seq, const int *token_pos, const int *seq_slot,
+                               const float *q_norm, const float *k_norm, float eps, const float *cos, const float *sin,
+                               void *k_pool, void *v_pool, const int *page_table, int table_width, int tokens_per_page,
+                               int *status, void *stream) {
+    if (M <= 0) return 0;
+    const int N = (n_heads + 2 * n_kv_heads) * 128;
+    if (M <= 256 || n_heads < 1 || n_kv_heads < 1 || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldo % 8 ||
+        (((uintptr_t)x | (uintptr_t)w | (uintptr_t)qkv | (uintptr_t)q_norm | (uintptr_t)k_norm | (uintptr_t)cos | (uintptr_t)sin |
+          (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) || !k_pool || !v_pool || !cos != !sin || tokens_per_page < 1)
+        ABK_REFUSE("gemm_tc_qkv: %d rows, %d + 2 x %d heads, K = %d are not what the fused kernel takes", M, n_heads, n_kv_heads, K);
+    CUtensorMap mx, mw;
+    int rc = tensor_map(x, M, K, ldx, TILE_P, &mx);
+    if (rc) return rc;
+    GemmTc g;
+    g.out = qkv, g.P = M, g.Q = N, g.K = K, g.stride_p = ldo, g.stride_q = 1;
+    g.k_blocks = (K + TILE_K - 1) / TILE_K, g.k_blocks_per_split = g.k_blocks, g.splits = 1;
+    g.partials = nullptr, g.tickets = nullptr, g.status = status, g.vec = 1, g.in_cluster = 0, g.weights_are_p = 0;
+    QkvEpilogue e;
+    e.token_seq = token_seq, e.token_pos = token_pos, e.seq_slot = seq_slot, e.q_norm = q_norm, e.k_norm = k_norm;
+    e.cos = cos, e.sin = sin, e.eps = eps, e.k_pool = (__nv_bfloat16 *)k_pool, e.v_pool = (__nv_bfloat16 *)v_pool;
+    e.cache.page_table = page_table, e.cache.table_width = table_width, e.cache.ring_pages = 0;
+    e.cache.tokens_per_page = tokens_per_page, e.n_heads = n_heads, e.n_kv_heads = n_kv_heads;
+    if (pairs_win(M, N) && !abk_pairs_off()) {
+        rc = tensor_map(w, N, K, ldw, 128, &mw);
+        if (rc) return rc;
+        const int m_tiles2 = (M + 2 * TILE_P - 1) / (2 * TILE_P);
+        return launch_pair<256, 5, __nv_bfloat16, EPI_QKV>(mx, mw, g, m_tiles2, m_tiles2 * ((N + 255) / 256), (cudaStream_t)stream, e);
+    }
+    rc = tensor_map(w, N, K, ldw, 256, &mw);
+    if (rc) return rc;
+    const int m_tiles = (M + TILE_P - 1) / TILE_P;
+    return launch_persistent<256, 3, __nv_bfloat16, EPI_QKV>(mx, mw, g, m_tiles, m_tiles * ((N + 255) / 256), (cudaStream_t)stream, e);
 }
 
 template <typename TO>

@@ -35,6 +35,9 @@ typedef int (*GemmTcFn)(const void *, const void *, void *, int, int, int, int, 
                         int *, int *, int, int, int, int, void *);
 typedef int (*GemmTcSwigluFn)(const void *, const void *, void *, int, int, int, long long, long long, long long, int *,
                               void *);
+typedef int (*GemmTcQkvFn)(const void *, const void *, void *, int, int, int, int, long long, long long, long long, const int *,
+                           const int *, const int *, const float *, const float *, float, const float *, const float *, void *,
+                           void *, const int *, int, int, int *, void *);
 typedef int (*AttnGenericFn)(const void *, long long, void *, int, int, int, int, int, float, int, const int *, const int *,
                              const int *, const int *, const int *, const void *, const void *, const int *, int, int, int,
                              const void *, const void *, long long, void *);
@@ -69,6 +72,7 @@ struct AbkFns {
     AttnDecodeRingFn attention_decode_ring;
     AttnDecodeFn attention_decode;
     AttnDecodeRingPrepareFn attention_decode_ring_prepare;
+    GemmTcQkvFn gemm_tc_qkv;
 };
 
 // ------------------------------------------------------------------ the model, bound once
@@ -118,7 +122,8 @@ struct AbkModel {
     float *halves;        // partial results of halved attention tiles
     int *halves_tickets, *attention_tickets;
     int dtype, hidden, vocab, n_blocks, n_entries, halves_pairs, attention_ticket_count;
-    int decode_prepares;  // decode attention prepares q, k and v itself where it can (parts/attention.py: DECODE_PREPARES)
+    int decode_prepares;   // decode attention prepares q, k and v itself where it can (parts/attention.py: DECODE_PREPARES)
+    int product_prepares;  // a prompt's q/k/v product prepares them in its epilogue where it can (PRODUCT_PREPARES)
 };
 
 // ------------------------------------------------------------------ one step
@@ -197,10 +202,22 @@ static int attention(const AbkModel &m, const AbkAttention &a, const AbkEntry &e
     const int n = s.n_rows, q_size = a.n_heads * a.head_dim, kv_size = a.n_kv_heads * a.head_dim;
     const long long row = q_size + 2 * kv_size;
     const bool writes = e.owns != 0, has_cache = e.k != nullptr;
-    if (writes) TRY(linear(m, a.qkv, s.xn, m.hidden, s.qkv, m.dtype, row, n, stream), "the q/k/v product");
-    else TRY(linear(m, a.q_only, s.xn, m.hidden, s.qkv, m.dtype, row, n, stream), "the q product");
     const int group = a.n_heads / a.n_kv_heads, hd = a.head_dim;
     const bool bf16 = m.dtype == ABK_BF16;
+    // a windowed cache keeps only the last keys; a prompt reads its keys from this step's own rows
+    const bool from_step = a.window > 0 && !s.is_decode;
+    // kernels/ops.py: gemm_tc_qkv_takes
+    const bool prepared = m.product_prepares && writes && !s.is_decode && !from_step && bf16 && n > 256 && hd == 128 &&
+                          e.ring_pages == 0 && a.qkv.n == row && (!a.cos || (a.rotary_dim == hd && !a.interleaved)) &&
+                          aligned16(a.q_norm) && aligned16(a.k_norm) && aligned16(a.cos) && aligned16(a.sin) && aligned16(e.k) &&
+                          aligned16(e.v) && row % 8 == 0 && aligned16(s.qkv) && tc_takes(s.xn, m.hidden, a.qkv);
+    if (prepared)
+        TRY(LAUNCH(f.gemm_tc_qkv, s.xn, a.qkv.w, s.qkv, n, a.n_heads, a.n_kv_heads, a.qkv.k, (long long)m.hidden, a.qkv.ldw, row,
+                   s.token_seq, s.token_pos, s.seq_slot, a.q_norm, a.k_norm, a.eps, a.cos, a.sin, e.k, e.v, e.table, e.table_width,
+                   e.tokens_per_page, m.kernel_status, stream),
+            "the q/k/v product");
+    else if (writes) TRY(linear(m, a.qkv, s.xn, m.hidden, s.qkv, m.dtype, row, n, stream), "the q/k/v product");
+    else TRY(linear(m, a.q_only, s.xn, m.hidden, s.qkv, m.dtype, row, n, stream), "the q product");
     const size_t decode_smem = (size_t)4 * 64 * hd * 2 + (size_t)4 * group * (hd + 2) * 4 + 64;
     const bool decode_takes = has_cache && (hd == 64 || hd == 128 || hd == 256) && e.tokens_per_page == 64 && decode_smem <= 200 * 1024;
     // kernels/ops.py: attention_decode_prepares
@@ -208,14 +225,12 @@ static int attention(const AbkModel &m, const AbkAttention &a, const AbkEntry &e
                           (!a.cos || (a.rotary_dim == hd && !a.interleaved)) && row % 8 == 0 && aligned16(s.qkv) &&
                           aligned16(a.q_norm) && aligned16(a.k_norm) && aligned16(a.cos) && aligned16(a.sin) && aligned16(e.k) &&
                           aligned16(e.v);
-    if (!prepares)
+    if (!prepares && !prepared)
         TRY(LAUNCH(f.qkv_prep, s.qkv, m.dtype, n, a.n_heads, a.n_kv_heads, a.head_dim, writes ? 0 : 1, s.token_seq, s.token_pos,
                    s.seq_slot, s.seq_len_after, a.q_norm, a.k_norm, a.eps, a.cos, a.sin, a.rotary_dim, a.interleaved,
                    writes ? e.k : nullptr, writes ? e.v : nullptr, writes ? e.table : nullptr, writes ? e.table_width : 0,
                    writes ? e.ring_pages : 0, writes ? e.tokens_per_page : 1, stream),
         "q/k/v preparation");
-    // a windowed cache keeps only the last keys; a prompt reads its keys from this step's own rows
-    const bool from_step = a.window > 0 && !s.is_decode;
     if (from_step && (s.any_continuation || !writes)) return fail(STEP_REFUSED_WINDOW, "windowed attention", entry);
     const bool prefill_takes = has_cache && (hd == 64 || hd == 128) && e.tokens_per_page == 64 && e.ring_pages == 0;
     const AbkLists *lists = a.lists >= 0 && a.lists < s.n_lists ? &s.lists[a.lists] : nullptr;

@@ -17,7 +17,7 @@ import torch
 
 from ..kernels import ops
 from ..kernels.build import load_module
-from ..parts.attention import DECODE_PREPARES, Attention
+from ..parts.attention import DECODE_PREPARES, PRODUCT_PREPARES, Attention
 from ..parts.attention_plan import AttentionLists
 from ..parts.block import PreNormBlock
 from ..parts.frame import PlainFrame
@@ -38,7 +38,8 @@ LAUNCHERS = [("embed", "elementwise", "abk_embed"), ("add_rmsnorm", "elementwise
              ("attention_prefill_tc", "attention_tc", "abk_attention_prefill_tc"),
              ("attention_decode_ring", "attention_decode_ring", "abk_attention_decode_ring"),
              ("attention_decode", "attention_decode", "abk_attention_decode"),
-             ("attention_decode_ring_prepare", "attention_decode_ring", "abk_attention_decode_ring_prepare")]
+             ("attention_decode_ring_prepare", "attention_decode_ring", "abk_attention_decode_ring_prepare"),
+             ("gemm_tc_qkv", "gemm_tc", "abk_gemm_tc_qkv")]
 
 
 class Fns(ctypes.Structure):
@@ -76,7 +77,8 @@ class ModelS(ctypes.Structure):
     _fields_ = [("fns", P), ("blocks", P), ("entries", P), ("embed", P), ("final_norm", Norm), ("head", Linear),
                 ("status", P), ("gemm_scratch", P), ("gemm_tickets", P), ("kernel_status", P), ("halves", P),
                 ("halves_tickets", P), ("attention_tickets", P), ("dtype", I), ("hidden", I), ("vocab", I),
-                ("n_blocks", I), ("n_entries", I), ("halves_pairs", I), ("attention_ticket_count", I), ("decode_prepares", I)]
+                ("n_blocks", I), ("n_entries", I), ("halves_pairs", I), ("attention_ticket_count", I), ("decode_prepares", I),
+                ("product_prepares", I)]
 
 
 class Lists(ctypes.Structure):
@@ -175,7 +177,7 @@ class CStep:
             _ptr(sc.attention_halves) if any128 else None, _ptr(sc.attention_halves_tickets) if any128 else None,
             _ptr(tickets), _dt(dtype), model.spec.hidden, model.spec.vocab, len(model.blocks),
             len(model.schedule), sc.attention_halves_pairs, tickets.numel() if tickets is not None else 0,
-            1 if DECODE_PREPARES else 0)
+            1 if DECODE_PREPARES else 0, 1 if PRODUCT_PREPARES else 0)
         self.qkv_width = max((s.n_heads + 2 * s.n_kv_heads) * s.head_dim for s in specs)
         self.att_width = max(s.n_heads * s.head_dim for s in specs)
         self.inter = max(b.ffn.spec.inter for b in model.blocks)

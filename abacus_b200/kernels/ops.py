@@ -242,6 +242,39 @@ def gemm_tc_swiglu(x, w_gate_up, act, m=None):
                                        _stream()), "gemm_tc_swiglu")
 
 
+def gemm_tc_qkv_takes(x, w_qkv, qkv, m, n_heads, n_kv_heads, head_dim, cache, q_norm, k_norm, cos, sin, rotary_dim, interleaved):
+    """Whether the q/k/v product of a step takes the preparation of its heads (per-head norm, rotation, keys and values
+    into the cache) into its epilogue: many rows, heads of 128, the rotation over the whole head in halves (or none),
+    a cache that keeps every page."""
+    tensors = [t for t in (q_norm, k_norm, cos, sin, cache.k, cache.v) if t is not None]
+    return (m > 256 and head_dim == 128 and qkv.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
+            and cache.ring_pages == 0 and w_qkv.shape[0] == (n_heads + 2 * n_kv_heads) * 128 == qkv.shape[1]
+            and (cos is None or (rotary_dim == head_dim and not interleaved))
+            and all(t.data_ptr() % 16 == 0 for t in tensors) and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0
+            and all(t is None or t.dtype == torch.float32 for t in (q_norm, k_norm, cos, sin))
+            and gemm_tc_takes(x, w_qkv, qkv))
+
+
+def gemm_tc_qkv(x, w_qkv, qkv, n_heads, n_kv_heads, batch, q_norm, k_norm, eps, cos, sin, cache, m=None):
+    """The q columns of qkv[:m] = the prepared q heads of x . w_qkv^T, and the prepared k and the v heads of every token
+    that belongs to a sequence into the cache (cache.LayerKV): the q/k/v product of a prompt on the tcgen05 tensor
+    cores with what stands between it and attention in its epilogue (src/model.c:299, 247-259). The k and v columns of
+    qkv are not written."""
+    _need_cuda(x, w_qkv, qkv)
+    lib = load_module("gemm_tc")
+    m = x.shape[0] if m is None else m
+    assert x.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16
+    assert x.shape[1] == w_qkv.shape[1] and x.stride(1) == 1 and w_qkv.stride(1) == 1 and qkv.stride(1) == 1
+    assert cache.k.shape[1:] == (n_kv_heads, cache.tokens_per_page, 128) and cache.k.is_contiguous() and cache.v.is_contiguous()
+    if cos is not None and batch.max_position >= cos.shape[0]:
+        raise KernelError(f"position {batch.max_position} is beyond the rotary table of {cos.shape[0]} positions")
+    _check(lib, lib.abk_gemm_tc_qkv(
+        _p(x), _p(w_qkv), _p(qkv), _i(m), _i(n_heads), _i(n_kv_heads), _i(x.shape[1]), _ll(x.stride(0)), _ll(w_qkv.stride(0)),
+        _ll(qkv.stride(0)), _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(q_norm), _p(k_norm), _f(eps or 0.0),
+        _p(cos), _p(sin), _p(cache.k), _p(cache.v), _p(cache.page_table), _i(cache.table_width), _i(cache.tokens_per_page),
+        _p(_Scratch.of(x.device).status), _stream()), "gemm_tc_qkv")
+
+
 def argmax(logits, out, n_rows=None):
     """out[r] = index of the first maximum of logits[r] (src/main.c:31-36)."""
     _need_cuda(logits, out)

@@ -18,6 +18,9 @@ from .linear import Linear
 # A decode step's attention kernel can norm and rotate q and k and write the new key and value to the cache itself: a
 # launch less in every layer. ABACUS_DECODE_PREPARES=0 keeps the preparation a kernel of its own (for comparison).
 DECODE_PREPARES = os.environ.get("ABACUS_DECODE_PREPARES", "1") != "0"
+# The q/k/v product of a long prompt step can do the same in its epilogue (heads of 128): a kernel and a pass over
+# q, k and v less. ABACUS_PRODUCT_PREPARES=0 keeps the preparation a kernel of its own (for comparison).
+PRODUCT_PREPARES = os.environ.get("ABACUS_PRODUCT_PREPARES", "1") != "0"
 
 
 @MIXERS.register("attention")
@@ -77,23 +80,33 @@ class Attention:
         qkv = ws.get("qkv", (n, self.q_size + 2 * self.kv_size), self.ctx.dtype)
         att = ws.get("att", (n, self.q_size), self.ctx.dtype)
         writes = cache.owns_storage
-        if writes:
+        rotary_dim = self.position.rotary_dim if self.position else 0
+        interleaved = self.position.interleaved if self.position else False
+        # A windowed cache keeps only the last keys; a prompt longer than that reads its keys from
+        # this step's own rows, which hold all of them when the sequences start at position 0.
+        from_step = s.window is not None and not batch.is_decode
+        w = self.qkv_proj.weight
+        prepared = False  # by the product's own kernel: a prompt's heads in its epilogue
+        if (PRODUCT_PREPARES and writes and not batch.is_decode and not from_step and w.dtype == torch.bfloat16
+                and ops.gemm_tc_qkv_takes(xn, w, qkv, n, s.n_heads, s.n_kv_heads, s.head_dim, cache.kv, self.q_norm,
+                                          self.k_norm, self.cos, self.sin, rotary_dim, interleaved)):
+            ops.gemm_tc_qkv(xn, w, qkv, s.n_heads, s.n_kv_heads, batch, self.q_norm, self.k_norm, s.qk_norm_eps,
+                            self.cos, self.sin, cache.kv, n)
+            prepared = True
+        elif writes:
             self.qkv_proj.forward(xn, qkv, n)
         else:  # keys and values are another entry's: only q is needed
             self.q_proj.forward(xn, qkv[:, :self.q_size], n)
-        rotary_dim = self.position.rotary_dim if self.position else 0
-        interleaved = self.position.interleaved if self.position else False
         prepare = None
-        if (DECODE_PREPARES and batch.is_decode and cache.kv is not None
+        if prepared:
+            pass
+        elif (DECODE_PREPARES and batch.is_decode and cache.kv is not None
                 and ops.attention_decode_prepares(qkv, s.n_heads, s.n_kv_heads, s.head_dim, cache.kv, self.q_norm,
                                                   self.k_norm, self.cos, self.sin, rotary_dim, interleaved)):
             prepare = dict(q_norm=self.q_norm, k_norm=self.k_norm, eps=s.qk_norm_eps, cos=self.cos, sin=self.sin, keep=writes)
         else:
             ops.qkv_prep(qkv, s.n_heads, s.n_kv_heads, s.head_dim, batch, self.q_norm, self.k_norm, s.qk_norm_eps,
                          self.cos, self.sin, rotary_dim, interleaved, cache.kv if writes else None, q_only=not writes)
-        # A windowed cache keeps only the last keys; a prompt longer than that reads its keys from
-        # this step's own rows, which hold all of them when the sequences start at position 0.
-        from_step = s.window is not None and not batch.is_decode
         if from_step and (batch.any_continuation or not writes):
             raise ops.KernelRefused("windowed attention takes several tokens of a sequence only at its start, "
                                     "and only with keys of its own")

@@ -513,6 +513,57 @@ def test_gemm_tc_pairs_of_ctas(ops, out_dtype):
     assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
 
 
+@pytest.mark.parametrize("hq, hkv, k, lens, norm, rotated", [
+    (16, 8, 1024, [2048], True, True),                  # pairs of CTAs, every tile full
+    (3, 1, 72, [300], True, True),                      # the persistent kernel; a last column tile of one head; a ragged K
+    (5, 2, 136, [700, 1, 64, 65, 470], True, True),     # pairs (9 heads: a last column tile of one head), ragged prompts
+    (4, 4, 264, [257, 130], False, True), (2, 1, 64, [400], True, False), (32, 8, 2560, [513, 300], True, True)])
+def test_gemm_tc_qkv_prepares_in_its_epilogue(ops, hq, hkv, k, lens, norm, rotated):
+    """The q/k/v product of a prompt step with the preparation of its heads in the epilogue, against the product and the
+    preparation's own kernel after it: the same bits in the q columns and in the cache. The second sequence starts at
+    position 37 (a continuation: its keys go to the middle of a page); three padding rows follow the last sequence."""
+    from abacus_b200.cache import CacheNeed, SequenceCache
+    from abacus_b200.engine.batch import Sequence, StepBatch
+    rng = np.random.default_rng(hq * 10 + k)
+    hd, rows = 128, sum(lens)
+    width = (hq + 2 * hkv) * hd
+    x = dev(bf(rng.standard_normal((rows + 3, k))), torch.bfloat16)
+    w = dev(bf(rng.standard_normal((width, k)) / np.sqrt(k)), torch.bfloat16)
+    qn = dev(1.0 + 0.3 * rng.standard_normal(hd), torch.float32) if norm else None
+    kn = dev(1.0 + 0.3 * rng.standard_normal(hd), torch.float32) if norm else None
+    angles = rng.uniform(0, 6.28, (4096, hd // 2))
+    cos = dev(np.cos(angles), torch.float32) if rotated else None
+    sin = dev(np.sin(angles), torch.float32) if rotated else None
+    results = []
+    for fused in (False, True):
+        cache = SequenceCache([CacheNeed(hkv, hd, None)], [None], 64 * 64, torch.bfloat16, "cuda", max_context=4096)
+        seqs = []
+        for i, n in enumerate(lens):
+            slot = cache.open_slot()
+            if i == 1:
+                cache.reserve(slot, 37), cache.advance(slot, 37)
+            seqs.append(Sequence(slot, [0] * n, cache.length[slot], []))
+            cache.reserve(slot, cache.length[slot] + n)
+        batch = StepBatch(rows + 3, len(lens) + 1, 0, "cuda", plans=[]).fill(seqs)
+        kv = cache.views[0].kv
+        qkv = torch.full((rows + 3, width), 3.0, dtype=torch.bfloat16, device="cuda")
+        if fused:
+            assert ops.gemm_tc_qkv_takes(x, w, qkv, rows + 3, hq, hkv, hd, kv, qn, kn, cos, sin, hd if rotated else 0, False)
+            ops.gemm_tc_qkv(x, w, qkv, hq, hkv, batch, qn, kn, 1e-5, cos, sin, kv)
+        else:
+            ops.gemm_tc(x, w, qkv)
+            ops.qkv_prep(qkv, hq, hkv, hd, batch, qn, kn, 1e-5, cos, sin, hd if rotated else 0, False, kv)
+        results.append((qkv[:rows, :hq * hd].clone(), kv.k.clone(), kv.v.clone(), kv.page_table.clone()))
+    (q_a, k_a, v_a, t_a), (q_b, k_b, v_b, t_b) = results
+    assert torch.equal(t_a, t_b)
+    assert torch.equal(q_a, q_b)
+    assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
+    assert float(k_a.float().abs().sum()) > 0 and float(q_a.float().abs().max()) > 0.1
+    assert ops.kernel_status(torch.device("cuda", 0)).tolist() == [0, 0, 0, 0]
+    small = torch.empty(200, width, dtype=torch.bfloat16, device="cuda")
+    assert not ops.gemm_tc_qkv_takes(x[:200], w, small, 200, hq, hkv, hd, kv, qn, kn, cos, sin, hd if rotated else 0, False)
+
+
 @pytest.mark.parametrize("m, n, k", [(1, 128, 64), (1, 1024, 2048), (8, 4096, 1024), (64, 1000, 72), (65, 192, 96),
                                       (300, 389, 96), (2048, 1024, 1024), (5, 151936, 128), (130, 70, 8), (1500, 4096, 264),
                                       # the down projections of the 4B and 8B shapes: K beyond the persistent kernel's 4,096
