@@ -946,8 +946,8 @@ extern "C" int abk_gemm_tc_qkv(const void *x, const void *w, void *qkv, int M, i
 template <typename TO>
 static int launch_bn(int bn, const CUtensorMap &mp, const CUtensorMap &mq, const GemmTc &g, dim3 grid, cudaStream_t s) {
     switch (bn) {
-    case 16: return launch<16, 4, TO>(mp, mq, g, grid, s);  // 72 KB: three CTAs share an SM
-    case 32: return launch<32, 4, TO>(mp, mq, g, grid, s);
+    case 16: return launch<16, 6, TO>(mp, mq, g, grid, s);  // 108 KB: two CTAs share an SM
+    case 32: return launch<32, 5, TO>(mp, mq, g, grid, s);
     case 64: return launch<64, 4, TO>(mp, mq, g, grid, s);
     case 128: return launch<128, 3, TO>(mp, mq, g, grid, s);
     case 256: return launch<256, 2, TO>(mp, mq, g, grid, s);
