@@ -151,8 +151,15 @@ def bench_decode_attention(args):
     cache, kv, b, qkv, out = _attention_setup(args.batch, args.context, args.heads, args.kv_heads, args.head_dim, 1)
     ws = Workspace(torch.device("cuda", 0))
     scale = args.head_dim ** -0.5
+    prepare = None
+    if args.prepares:  # the kernel norms and rotates q and k and writes the new key and value itself
+        hd = args.head_dim
+        qn, kn = torch.ones(hd, device="cuda"), torch.ones(hd, device="cuda")
+        pos = torch.arange(args.context + 64, device="cuda", dtype=torch.float32)[:, None]
+        inv = 1.0 / (1e6 ** (torch.arange(0, hd, 2, device="cuda", dtype=torch.float32) / hd))
+        prepare = dict(q_norm=qn, k_norm=kn, eps=1e-6, cos=torch.cos(pos * inv).contiguous(), sin=torch.sin(pos * inv).contiguous(), keep=True)
     fn = lambda: ops.attention_decode(qkv, out, args.heads, args.kv_heads, args.head_dim, scale, None, b, kv, ws,
-                                      simt=args.simt)
+                                      simt=args.simt, prepare=prepare)
     us, best = timed_graph_flushed(fn)
     nbytes = args.batch * args.context * args.kv_heads * args.head_dim * 2 * 2
     return {"kernel": "attention_decode", "batch": args.batch, "context": args.context, "us": round(us, 2),
@@ -190,6 +197,33 @@ def bench_qkv_prep(args):
             "GB/s": round(nbytes / us / 1e3, 1)}
 
 
+def bench_qkv_product(args):
+    """The q/k/v product of one prompt step of `tokens` rows (batch sequences) against a matrix of --k columns, with the
+    preparation of its heads in the epilogue (or, with --separate, as the product and the preparation kernel after it)."""
+    from . import ops
+    heads, kv_heads, hd = args.heads, args.kv_heads, args.head_dim
+    cache, kv, b, qkv, out = _attention_setup(args.batch, args.tokens, heads, kv_heads, hd, args.tokens)
+    rows, width = args.batch * args.tokens, (heads + 2 * kv_heads) * hd
+    x = torch.randn(rows, args.k, device="cuda").to(torch.bfloat16)
+    copies = max(2, min(16, (160 << 20) // (width * args.k * 2) + 1))
+    ws = [(torch.randn(width, args.k, device="cuda") / args.k ** 0.5).to(torch.bfloat16) for _ in range(copies)]
+    qn, kn = torch.ones(hd, device="cuda"), torch.ones(hd, device="cuda")
+    pos = torch.arange(args.tokens + 64, device="cuda", dtype=torch.float32)[:, None]
+    inv = 1.0 / (1e6 ** (torch.arange(0, hd, 2, device="cuda", dtype=torch.float32) / hd))
+    cos, sin = torch.cos(pos * inv).contiguous(), torch.sin(pos * inv).contiguous()
+    if args.separate:
+        fns = []
+        for w in ws:
+            fns += [lambda w=w: ops.gemm_tc(x, w, qkv), lambda: ops.qkv_prep(qkv, heads, kv_heads, hd, b, qn, kn, 1e-6, cos, sin, hd, False, kv)]
+        us, best = timed_graph(fns)
+        us, best = 2 * us, 2 * best
+    else:
+        assert ops.gemm_tc_qkv_takes(x, ws[0], qkv, rows, heads, kv_heads, hd, kv, qn, kn, cos, sin, hd, False)
+        us, best = timed_graph([lambda w=w: ops.gemm_tc_qkv(x, w, qkv, heads, kv_heads, b, qn, kn, 1e-6, cos, sin, kv) for w in ws])
+    return {"kernel": "q/k/v product" + (" + qkv_prep" if args.separate else " that prepares"), "rows": rows, "n": width, "k": args.k,
+            "us": round(us, 2), "best_us": round(best, 2), "TFLOP/s": round(2.0 * rows * width * args.k / us / 1e6, 2)}
+
+
 def bench_argmax(args):
     from . import ops
     copies = max(2, (160 << 20) // (args.rows * args.vocab * 4) + 1)
@@ -213,7 +247,7 @@ def bench_add_rmsnorm(args):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention", "qkv_prep", "argmax", "add_rmsnorm"])
+    ap.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention", "qkv_prep", "qkv_product", "argmax", "add_rmsnorm"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
@@ -233,13 +267,15 @@ def main(argv=None):
     ap.add_argument("--width", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--rows-kernel", action="store_true", help="gemm: the weight-streaming kernel for m <= 16")
+    ap.add_argument("--separate", action="store_true", help="qkv_product: the product and the preparation as two kernels")
+    ap.add_argument("--prepares", action="store_true", help="decode_attention: q, k and v are prepared in the attention kernel")
     ap.add_argument("--simt", action="store_true", help="decode_attention: the CUDA-core kernel")
     ap.add_argument("--with-norm", action="store_true", help="gemm: alternate with an add_rmsnorm, as a model step does")
     args = ap.parse_args(argv)
     if args.kernel in ("prefill_attention", "qkv_prep") and "--batch" not in (argv or sys.argv):
         args.batch = 1
     fn = {"gemm": bench_gemm, "decode_attention": bench_decode_attention, "prefill_attention": bench_prefill_attention,
-          "qkv_prep": bench_qkv_prep, "argmax": bench_argmax, "add_rmsnorm": bench_add_rmsnorm}[args.kernel]
+          "qkv_prep": bench_qkv_prep, "qkv_product": bench_qkv_product, "argmax": bench_argmax, "add_rmsnorm": bench_add_rmsnorm}[args.kernel]
     print(json.dumps(fn(args)))
     return 0
 
