@@ -242,3 +242,49 @@ def test_the_step_function_in_c_launches_what_the_parts_would(tmp_path, name, dt
         for a, b in zip(results[0], other):
             assert torch.equal(a, b)
 
+
+
+def test_preparing_q_k_v_in_the_neighbouring_kernels_changes_no_bit(tmp_path, monkeypatch):
+    """In bfloat16 the step between the q/k/v product and attention (per-head norm, rotation, cache write) runs in the
+    product's epilogue for long prompt steps and inside the attention kernel for decode steps. With both switched off
+    it is a kernel of its own. Prompts of 300 and 281 tokens, a continuation by 270 and 1 tokens and decode steps give
+    the same bits either way, through the C walker and through the parts."""
+    from abacus_b200.engine import Engine, cstep, load_model
+    from abacus_b200.kernels import ops
+    from abacus_b200.parts import attention
+    folder = folder_of(tmp_path, "D")
+    model = load_model(folder, "bfloat16")
+    rng = np.random.default_rng(6)
+    vocab = TINY["D"]["cfg"]["vocab_size"]
+    prompts = [random_tokens(rng, n, vocab) for n in (300, 281)]
+    more = [random_tokens(rng, n, vocab) for n in (270, 1)]
+    single = [random_tokens(rng, 2, vocab) for _ in range(4)]
+
+    def run(engine):
+        out, slots = [], [engine.open() for _ in prompts]
+        out.append(engine.step([(s, p, [0, len(p) - 1]) for s, p in zip(slots, prompts)]).clone())
+        out.append(engine.step([(s, m, [len(m) - 1]) for s, m in zip(slots, more)]).clone())
+        for k in range(4):
+            out.append(engine.step([(s, [int(t)], [0]) for s, t in zip(slots, single[k])]).clone())
+        for s in slots:
+            engine.close(s)
+        engine.check_status()
+        return out
+
+    results, launches = [], []
+    for fused in (True, False):
+        for module in (attention, cstep):
+            monkeypatch.setattr(module, "DECODE_PREPARES", fused)
+            monkeypatch.setattr(module, "PRODUCT_PREPARES", fused)
+        for c_step in (True, False):
+            engine = Engine(model, max_tokens=64 * 24, use_graphs=False)
+            if not c_step:
+                engine.cstep = None
+            before = ops.LAUNCHES
+            results.append(run(engine))
+            launches.append(ops.LAUNCHES - before)
+    for other in results[1:]:
+        for a, b in zip(results[0], other):
+            assert torch.equal(a, b)
+    # the preparation's own kernel is one launch more per layer and step: 2 layers x 6 steps
+    assert launches[0] == launches[1] and launches[2] == launches[3] == launches[0] + 2 * 6, launches
