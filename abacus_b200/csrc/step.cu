@@ -3,7 +3,9 @@
 // abacus's forward() is C (src/model.c:286-327): embedding, then for each layer add_norm, the q/k/v product,
 // rotate_and_cache, attention, the output product, add_norm, gate/up, SwiGLU, down, then the last norm and the
 // output matrix on the wanted rows. This is that function for a batch of sequences on the GPU: the same order, each
-// line a kernel launch. The kernels live in libraries of their own; their launchers' addresses are handed in once
+// line a kernel launch (rotate_and_cache is a launch of its own only where neither neighbour takes it in: the q/k/v
+// product of a long prompt step does it in its epilogue, decode attention in its own kernel). The kernels live in
+// libraries of their own; their launchers' addresses are handed in once
 // (AbkFns), as are the model's matrices, sizes and constants (AbkModel), so that a step costs the host one call
 // instead of one per kernel (a few hundred, at some ten microseconds each from Python).
 //
